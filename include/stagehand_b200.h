@@ -1,0 +1,249 @@
+/*
+ * stagehand_b200 -- C ABI of the B200-native SquareQ weight-streaming path.
+ *
+ * Plain C types only: pointers, sizes, integer handles.  Streams and events
+ * cross the boundary as uint64_t holding a cudaStream_t / cudaEvent_t, the same
+ * convention the reference's native crates use for streams coming from
+ * torch.cuda.Stream.cuda_stream (vmm_src/python.rs:64-73).
+ *
+ * Every function returns an int32 status: 0 = ok, negative = SH_ERR_*.  The
+ * text of the last failure on the calling thread is read with sh_last_error().
+ * No function calls back into the host language, takes its interpreter lock,
+ * or blocks -- except the explicit *_wait / *_synchronize calls, which take a
+ * deadline in milliseconds and return SH_ERR_TIMEOUT when it passes.
+ *
+ * Each declaration names the reference interface it replaces (paths relative
+ * to the reference project).
+ */
+#ifndef STAGEHAND_B200_H
+#define STAGEHAND_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SH_ABI_VERSION 1
+
+/* status codes */
+#define SH_OK                 0
+#define SH_ERR_INVALID_ARG   -1
+#define SH_ERR_OOM           -2
+#define SH_ERR_CUDA          -3
+#define SH_ERR_TIMEOUT       -4
+#define SH_ERR_BUSY          -5   /* "not ready yet" from the query calls */
+#define SH_ERR_UNSUPPORTED   -6
+
+/* what a descriptor asks the block kernel to produce */
+#define SH_KIND_DEQUANT_I8    0   /* int8 rows * fp32 row scale (- fp32 row zero point) -> out dtype */
+#define SH_KIND_CAST_F32      1   /* fp32 vector -> out dtype (bias, norm weights)                  */
+#define SH_KIND_COPY          2   /* raw bytes (already in the out dtype)                           */
+#define SH_KIND_ZERO          3   /* zero fill                                                      */
+
+/* runtime dtype of the block's VRAM slab */
+#define SH_DT_BF16            0
+#define SH_DT_F16             1
+#define SH_DT_F32             2
+
+/* descriptor flags */
+#define SH_DESC_PEER_SOURCE   1u  /* source bytes live in another GPU's memory: plain loads only */
+
+/*
+ * One parameter of a block.  All *_off fields are byte offsets: sources from
+ * the start of the packed image, dst_off from the start of the output slab.
+ *
+ *   DEQUANT_I8: rows x cols int8 at src_off with row stride ld bytes; rows fp32
+ *               scales at scale_off; rows fp32 zero points at zp_off, or
+ *               zp_off = -1 when every zero point is zero.  Output is dense
+ *               [rows, cols] in the out dtype at dst_off.
+ *   CAST_F32:   cols fp32 values at src_off -> cols out-dtype values at dst_off.
+ *   COPY:       cols bytes from src_off to dst_off.
+ *   ZERO:       cols bytes of zero at dst_off.
+ *
+ * Replaces, per parameter, one iteration of the layout loop in
+ * src/stagehand/scheduler.py:263-325.
+ */
+typedef struct ShParamDesc {
+    int32_t  kind;
+    uint32_t flags;
+    int64_t  src_off;
+    int64_t  scale_off;
+    int64_t  zp_off;
+    int64_t  dst_off;
+    int64_t  rows;
+    int64_t  cols;
+    int64_t  ld;
+} ShParamDesc;
+
+typedef struct ShDeviceInfo {
+    int32_t device;
+    int32_t cc_major;
+    int32_t cc_minor;
+    int32_t sm_count;
+    int64_t total_mem_bytes;
+    int64_t l2_bytes;
+} ShDeviceInfo;
+
+typedef struct ShStats {
+    int64_t kernel_launches;      /* block-kernel launches since sh_init / sh_stats_reset   */
+    int64_t elements_dequantised; /* int8 weights converted                                   */
+    int64_t h2d_copies;           /* host-to-device copies issued                             */
+    int64_t h2d_bytes;
+    int64_t peer_copies;          /* device-to-device copies issued (local or peer source)    */
+    int64_t peer_bytes;
+    int64_t kernel_status_errors; /* launches whose device status word came back non-zero     */
+} ShStats;
+
+/* ── library ─────────────────────────────────────────────────────────── */
+
+/* ABI version of the loaded library (SH_ABI_VERSION it was built with). */
+int32_t sh_abi_version(void);
+
+/* Copies the last error text of the calling thread into buf (NUL-terminated). Returns its length. */
+int32_t sh_last_error(char* buf, int32_t buf_len);
+
+/*
+ * Selects the device for the calling thread and checks that it can run the
+ * sm_100a kernels.  Replaces TransferEngine::initialize's cudaSetDevice
+ * (turbo_src/engine.rs:102-126) and SlabAllocator::new(device) (vmm_src/allocator.rs:80-137).
+ */
+int32_t sh_init(int32_t device);
+int32_t sh_shutdown(void);
+int32_t sh_device_info(int32_t device, ShDeviceInfo* out);
+int32_t sh_stats(ShStats* out);
+int32_t sh_stats_reset(void);
+
+/* ── streams and events ──────────────────────────────────────────────── */
+
+/*
+ * Non-blocking stream with a priority (negative = higher), as the reference's
+ * copy stream (src/stagehand/__init__.py:159-161; turbo_src/engine.rs:127-130).
+ */
+int32_t sh_stream_create(int32_t priority, uint64_t* stream_out);
+int32_t sh_stream_destroy(uint64_t stream);
+int32_t sh_stream_synchronize(uint64_t stream, int32_t timeout_ms);
+int32_t sh_stream_wait_event(uint64_t stream, uint64_t event);
+
+/*
+ * Events: record / query / bounded wait.  Replace torch.cuda.Event use in
+ * src/stagehand/transfer.py:129-135,:188,:203 and cudaEvent* in turbo_src/cuda_ffi.rs:49-54.
+ * sh_event_query returns SH_OK when complete and SH_ERR_BUSY when not.
+ * sh_event_wait polls until the deadline instead of blocking without bound.
+ */
+int32_t sh_event_create(int32_t enable_timing, uint64_t* event_out);
+int32_t sh_event_destroy(uint64_t event);
+int32_t sh_event_record(uint64_t event, uint64_t stream);
+int32_t sh_event_query(uint64_t event);
+int32_t sh_event_wait(uint64_t event, int32_t timeout_ms);
+int32_t sh_event_elapsed_ms(uint64_t start, uint64_t stop, float* ms_out);
+
+/* ── memory ──────────────────────────────────────────────────────────── */
+
+/*
+ * Page-locked host memory for packed block images.  Replaces cudaMallocHost /
+ * cudaFreeHost in turbo_src/engine.rs:132-138,:396-415 and the pin_memory slabs
+ * of src/stagehand/pool.py:86-101.
+ */
+int32_t sh_host_alloc(size_t bytes, void** ptr_out);
+int32_t sh_host_free(void* ptr);
+/* Page-lock / unlock memory the caller already owns (e.g. a torch CPU tensor). */
+int32_t sh_host_register(void* ptr, size_t bytes);
+int32_t sh_host_unregister(void* ptr);
+
+/*
+ * Device memory outside any caching allocator, for INT8 images that stay
+ * resident in HBM (one GPU's share of a sharded model).  Exportable with
+ * sh_ipc_export.  No reference counterpart beyond cudaMalloc in turbo_src/cuda_ffi.rs:31.
+ */
+int32_t sh_device_alloc(size_t bytes, void** ptr_out);
+int32_t sh_device_free(void* ptr);
+
+/*
+ * Row-strided host copy on several threads: rows x row_bytes from src (stride
+ * src_ld) to dst (stride dst_ld).  Builds a packed image from slab tensors
+ * whose rows are padded.  Replaces the per-parameter host copies of
+ * TransferEngine::stage_block_to_pinned (turbo_src/engine.rs:159-176).
+ */
+int32_t sh_pack_rows(void* dst, int64_t dst_ld, const void* src, int64_t src_ld,
+                     int64_t rows, int64_t row_bytes, int32_t n_threads);
+
+/* ── data movement ───────────────────────────────────────────────────── */
+
+/*
+ * Asynchronous host-to-device copy of a packed image on `stream`.  Replaces
+ * gpu_dest.copy_(src, non_blocking=True) in src/stagehand/transfer.py:132-133 and
+ * cudaMemcpyAsync in turbo_src/engine.rs:202-231.
+ */
+int32_t sh_copy_h2d_async(void* dst_dev, const void* src_host, size_t bytes, uint64_t stream);
+
+/*
+ * Asynchronous device-to-device copy of a packed image into a local staging
+ * slab; src may be a peer GPU's memory opened with sh_ipc_open (copy engines,
+ * no SM use).  The reference is single-GPU: no counterpart.
+ */
+int32_t sh_pull_block_async(void* dst_local, const void* src_dev, size_t bytes, uint64_t stream);
+
+/* Enable direct access from the current device to `peer_device` (idempotent). */
+int32_t sh_peer_enable(int32_t peer_device);
+
+/* 64-byte inter-process handle of a sh_device_alloc allocation, and its peer-side mapping. */
+int32_t sh_ipc_export(void* dev_ptr, uint8_t handle_out[64]);
+int32_t sh_ipc_open(const uint8_t handle[64], void** dev_ptr_out);
+int32_t sh_ipc_close(void* dev_ptr);
+
+/* ── the block kernel ────────────────────────────────────────────────── */
+
+/*
+ * Launches the sm_100a block kernel on `stream`: for every descriptor, reads
+ * its source inside packed_dev[0, packed_bytes) and writes its destination
+ * inside out_dev[0, out_bytes) in `out_dtype`.  Descriptors are validated on the
+ * host first (bounds, alignment of the element size); an invalid one fails the
+ * call with SH_ERR_INVALID_ARG and nothing is launched.  `status_dev` is either
+ * NULL or a device int32 the kernel ORs error bits into (it never faults on a
+ * bad descriptor or a scale fetch that does not complete: it records and skips).
+ *
+ * `descs` is host memory and is consumed before the call returns.
+ *
+ * Replaces the SquareQ host dequant _copy_squareq_backed_params_into_buffer
+ * (src/stagehand/scheduler.py:243-325) -- the output bytes are what that
+ * function writes into the pinned slab, produced directly in VRAM.
+ */
+int32_t sh_dequant_block_async(const ShParamDesc* descs, int32_t n_descs,
+                               const void* packed_dev, size_t packed_bytes,
+                               void* out_dev, size_t out_bytes, int32_t out_dtype,
+                               uint64_t stream, int32_t* status_dev);
+
+/*
+ * One block from HOST memory to runtime-dtype weights in VRAM:
+ *   copy_stream:    H2D copy of the packed image into staging_dev, record ev_copied
+ *   dequant_stream: wait ev_copied, run the block kernel into out_dev, record ev_ready
+ * ev_copied / ev_ready may be 0 (then no event is recorded; with ev_copied = 0 and
+ * two different streams the call fails, because the kernel could not be ordered
+ * after the copy).  The caller makes its compute stream wait on ev_ready.
+ *
+ * Replaces _stage_block_to_host + submit_h2d for a SquareQ block
+ * (src/stagehand/scheduler.py:953-987, src/stagehand/transfer.py:108-143).
+ */
+int32_t sh_stream_block_async(const ShParamDesc* descs, int32_t n_descs,
+                              const void* packed_host, size_t packed_bytes,
+                              void* staging_dev, void* out_dev, size_t out_bytes, int32_t out_dtype,
+                              uint64_t copy_stream, uint64_t dequant_stream,
+                              uint64_t ev_copied, uint64_t ev_ready, int32_t* status_dev);
+
+/*
+ * Per-launch device timing of the block kernel (CUDA events on the launching
+ * stream).  While enabled every launch is bracketed by a pair of timing events;
+ * sh_profile_collect waits for them (bounded) and returns the sums since the
+ * last collect.  Replaces nothing in the reference (its telemetry has a
+ * copy_time_ms field that is never filled, src/stagehand/telemetry.py:31).
+ */
+int32_t sh_profile_enable(int32_t on);
+int32_t sh_profile_collect(double* kernel_ms_out, int64_t* launches_out, int64_t* elements_out,
+                           int64_t* bytes_out, int32_t timeout_ms);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* STAGEHAND_B200_H */

@@ -1,0 +1,57 @@
+"""Runtime configuration.
+
+Field names, types and defaults are those of the reference's ``StagehandConfig``
+(``src/stagehand/config.py:9-46``) so existing construction code keeps working.
+The three trailing fields are additions of this implementation; all are optional.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+__all__ = ["StagehandConfig"]
+
+
+@dataclass
+class StagehandConfig:
+    # master switch (declared by the reference, read nowhere there either)
+    stagehand_enabled: bool = True
+
+    # host memory
+    pinned_pool_mb: int = 8192
+    pinned_slab_mb: int = 256
+    pinned_slab_alignment: int = 512
+    # VRAM watermarks (MB of allocator-visible memory)
+    vram_high_watermark_mb: int = 22000
+    vram_low_watermark_mb: int = 18000
+
+    # transfers
+    max_inflight_transfers: int = 2
+    copy_stream_priority: int = -1
+
+    # scheduling
+    policy: str = "static"
+    prefetch_window_blocks: int = 3
+    eviction_cooldown_steps: int = 2
+
+    # numeric guards
+    strict_bf16: bool = True
+    fail_on_dtype_promotion: bool = True
+    nan_inf_check: bool = True
+
+    # telemetry
+    telemetry_enabled: bool = True
+    telemetry_interval_steps: int = 10
+    telemetry_file: str = "stagehand_telemetry.jsonl"
+
+    debug_trace: bool = False
+
+    # ── additions (SquareQ INT8 streaming path) ──────────────────────
+    # Budget, in MiB of page-locked host memory, for keeping packed INT8 block
+    # images resident between steps so a reload is a single DMA with no host
+    # work.  -1 = as much as half of physical RAM; 0 = never keep an image.
+    packed_image_cache_mb: int = -1
+    # INT8 staging slabs in VRAM (copies in flight ahead of their dequant).
+    # 0 = prefetch_window_blocks + 1.
+    device_staging_slabs: int = 0
+    # Host threads used to pack an image that is not cached.
+    pack_threads: int = 8

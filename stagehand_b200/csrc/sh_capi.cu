@@ -1,0 +1,472 @@
+// C ABI of the SquareQ streaming path (declarations and reference citations:
+// include/stagehand_b200.h).  Thin, non-blocking wrappers over the CUDA runtime
+// plus the launcher of the block kernel.  No torch types, no interpreter calls.
+#include "../../include/stagehand_b200.h"
+#include "sq_block_kernel.cuh"
+
+#include <algorithm>
+#include <atomic>
+#include <chrono>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <thread>
+#include <vector>
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+    const int code = (e == cudaErrorMemoryAllocation) ? SH_ERR_OOM : SH_ERR_CUDA;
+    return fail(code, "%s: %s (%d)", what, cudaGetErrorString(e), static_cast<int>(e));
+}
+
+#define SH_CUDA(call, what)                                   \
+    do {                                                      \
+        cudaError_t e__ = (call);                             \
+        if (e__ != cudaSuccess) return cuda_fail(e__, what);  \
+    } while (0)
+
+inline cudaStream_t as_stream(uint64_t s) { return reinterpret_cast<cudaStream_t>(static_cast<uintptr_t>(s)); }
+inline cudaEvent_t as_event(uint64_t e) { return reinterpret_cast<cudaEvent_t>(static_cast<uintptr_t>(e)); }
+
+struct Counters {
+    std::atomic<int64_t> launches{0}, elements{0}, h2d_copies{0}, h2d_bytes{0}, peer_copies{0}, peer_bytes{0},
+        status_errors{0};
+} g_ctr;
+
+// per-launch timing records
+struct ProfRecord {
+    cudaEvent_t start, stop;
+    int64_t elements, bytes;
+};
+std::mutex g_prof_mu;
+std::vector<ProfRecord> g_prof_pending;
+std::vector<cudaEvent_t> g_prof_free;
+std::atomic<int> g_prof_on{0};
+
+cudaEvent_t prof_event() {
+    if (!g_prof_free.empty()) {
+        cudaEvent_t e = g_prof_free.back();
+        g_prof_free.pop_back();
+        return e;
+    }
+    cudaEvent_t e = nullptr;
+    if (cudaEventCreate(&e) != cudaSuccess) return nullptr;
+    return e;
+}
+
+// Polls an event until done or until the deadline; never blocks without bound.
+int wait_event_bounded(cudaEvent_t ev, int timeout_ms) {
+    const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms < 0 ? 0 : timeout_ms);
+    int spins = 0;
+    for (;;) {
+        const cudaError_t q = cudaEventQuery(ev);
+        if (q == cudaSuccess) return SH_OK;
+        if (q != cudaErrorNotReady) return cuda_fail(q, "cudaEventQuery");
+        if (std::chrono::steady_clock::now() >= deadline) return fail(SH_ERR_TIMEOUT, "event not complete after %d ms", timeout_ms);
+        if (++spins > 200) std::this_thread::sleep_for(std::chrono::microseconds(50));
+    }
+}
+
+int launch_block(const ShParamDesc* descs, int32_t n, const void* packed, size_t packed_bytes, void* out,
+                 size_t out_bytes, int32_t out_dtype, cudaStream_t stream, int32_t* status_dev) {
+    if (n < 0 || (n > 0 && descs == nullptr)) return fail(SH_ERR_INVALID_ARG, "null descriptor array");
+    if (n == 0) return SH_OK;
+    if (out == nullptr) return fail(SH_ERR_INVALID_ARG, "null output slab");
+    const int max_plans = (n + sq::kMaxDescs - 1) / sq::kMaxDescs;
+    std::vector<sq::BlockPlan> plans(static_cast<size_t>(max_plans));
+    int n_plans = 0;
+    int64_t elements = 0, traffic = 0;
+    char err[256];
+    const int rc = sq::build_plans(descs, n, packed, packed_bytes, out, out_bytes, out_dtype, plans.data(), &n_plans,
+                                   &elements, &traffic, err, sizeof(err));
+    if (rc != SH_OK) return fail(rc, "%s", err);
+
+    ProfRecord rec{nullptr, nullptr, elements, traffic};
+    const bool prof = g_prof_on.load(std::memory_order_relaxed) != 0;
+    if (prof) {
+        std::lock_guard<std::mutex> lk(g_prof_mu);
+        rec.start = prof_event();
+        rec.stop = prof_event();
+    }
+    if (rec.start) cudaEventRecord(rec.start, stream);
+    for (int p = 0; p < n_plans; ++p) {
+        const cudaError_t e = sq::launch_plan(plans[p], out_dtype, stream, status_dev);
+        if (e != cudaSuccess) return cuda_fail(e, "block kernel launch");
+        g_ctr.launches.fetch_add(1, std::memory_order_relaxed);
+    }
+    if (rec.stop) cudaEventRecord(rec.stop, stream);
+    if (prof && rec.start && rec.stop) {
+        std::lock_guard<std::mutex> lk(g_prof_mu);
+        g_prof_pending.push_back(rec);
+    }
+    g_ctr.elements.fetch_add(elements, std::memory_order_relaxed);
+    return SH_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t sh_abi_version(void) { return SH_ABI_VERSION; }
+
+int32_t sh_last_error(char* buf, int32_t buf_len) {
+    const int32_t n = static_cast<int32_t>(strlen(g_err));
+    if (buf != nullptr && buf_len > 0) {
+        const int32_t c = std::min(n, buf_len - 1);
+        memcpy(buf, g_err, static_cast<size_t>(c));
+        buf[c] = '\0';
+    }
+    return n;
+}
+
+int32_t sh_init(int32_t device) {
+    int count = 0;
+    SH_CUDA(cudaGetDeviceCount(&count), "cudaGetDeviceCount");
+    if (device < 0 || device >= count) return fail(SH_ERR_INVALID_ARG, "device %d out of range (0..%d)", device, count - 1);
+    SH_CUDA(cudaSetDevice(device), "cudaSetDevice");
+    cudaDeviceProp prop;
+    SH_CUDA(cudaGetDeviceProperties(&prop, device), "cudaGetDeviceProperties");
+    if (prop.major != 10)
+        return fail(SH_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library carries sm_100a code only", device, prop.major,
+                    prop.minor);
+    return SH_OK;
+}
+
+int32_t sh_shutdown(void) {
+    std::lock_guard<std::mutex> lk(g_prof_mu);
+    for (auto& r : g_prof_pending) {
+        cudaEventDestroy(r.start);
+        cudaEventDestroy(r.stop);
+    }
+    g_prof_pending.clear();
+    for (auto e : g_prof_free) cudaEventDestroy(e);
+    g_prof_free.clear();
+    return SH_OK;
+}
+
+int32_t sh_device_info(int32_t device, ShDeviceInfo* out) {
+    if (out == nullptr) return fail(SH_ERR_INVALID_ARG, "null out");
+    cudaDeviceProp prop;
+    SH_CUDA(cudaGetDeviceProperties(&prop, device), "cudaGetDeviceProperties");
+    out->device = device;
+    out->cc_major = prop.major;
+    out->cc_minor = prop.minor;
+    out->sm_count = prop.multiProcessorCount;
+    out->total_mem_bytes = static_cast<int64_t>(prop.totalGlobalMem);
+    out->l2_bytes = static_cast<int64_t>(prop.l2CacheSize);
+    return SH_OK;
+}
+
+int32_t sh_stats(ShStats* out) {
+    if (out == nullptr) return fail(SH_ERR_INVALID_ARG, "null out");
+    out->kernel_launches = g_ctr.launches.load();
+    out->elements_dequantised = g_ctr.elements.load();
+    out->h2d_copies = g_ctr.h2d_copies.load();
+    out->h2d_bytes = g_ctr.h2d_bytes.load();
+    out->peer_copies = g_ctr.peer_copies.load();
+    out->peer_bytes = g_ctr.peer_bytes.load();
+    out->kernel_status_errors = g_ctr.status_errors.load();
+    return SH_OK;
+}
+
+int32_t sh_stats_reset(void) {
+    g_ctr.launches = 0; g_ctr.elements = 0; g_ctr.h2d_copies = 0; g_ctr.h2d_bytes = 0;
+    g_ctr.peer_copies = 0; g_ctr.peer_bytes = 0; g_ctr.status_errors = 0;
+    return SH_OK;
+}
+
+// ── streams and events ──────────────────────────────────────────────────
+
+int32_t sh_stream_create(int32_t priority, uint64_t* stream_out) {
+    if (stream_out == nullptr) return fail(SH_ERR_INVALID_ARG, "null stream_out");
+    int lo = 0, hi = 0;
+    SH_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi), "cudaDeviceGetStreamPriorityRange");
+    const int prio = std::max(hi, std::min(lo, static_cast<int>(priority)));   // hi is the numerically smallest
+    cudaStream_t s = nullptr;
+    SH_CUDA(cudaStreamCreateWithPriority(&s, cudaStreamNonBlocking, prio), "cudaStreamCreateWithPriority");
+    *stream_out = static_cast<uint64_t>(reinterpret_cast<uintptr_t>(s));
+    return SH_OK;
+}
+
+int32_t sh_stream_destroy(uint64_t stream) {
+    SH_CUDA(cudaStreamDestroy(as_stream(stream)), "cudaStreamDestroy");
+    return SH_OK;
+}
+
+int32_t sh_stream_synchronize(uint64_t stream, int32_t timeout_ms) {
+    cudaEvent_t ev = nullptr;
+    SH_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming), "cudaEventCreate");
+    cudaError_t e = cudaEventRecord(ev, as_stream(stream));
+    if (e != cudaSuccess) {
+        cudaEventDestroy(ev);
+        return cuda_fail(e, "cudaEventRecord");
+    }
+    const int rc = wait_event_bounded(ev, timeout_ms);
+    cudaEventDestroy(ev);
+    return rc;
+}
+
+int32_t sh_stream_wait_event(uint64_t stream, uint64_t event) {
+    SH_CUDA(cudaStreamWaitEvent(as_stream(stream), as_event(event), 0), "cudaStreamWaitEvent");
+    return SH_OK;
+}
+
+int32_t sh_event_create(int32_t enable_timing, uint64_t* event_out) {
+    if (event_out == nullptr) return fail(SH_ERR_INVALID_ARG, "null event_out");
+    cudaEvent_t ev = nullptr;
+    SH_CUDA(cudaEventCreateWithFlags(&ev, enable_timing ? cudaEventDefault : cudaEventDisableTiming), "cudaEventCreate");
+    *event_out = static_cast<uint64_t>(reinterpret_cast<uintptr_t>(ev));
+    return SH_OK;
+}
+
+int32_t sh_event_destroy(uint64_t event) {
+    SH_CUDA(cudaEventDestroy(as_event(event)), "cudaEventDestroy");
+    return SH_OK;
+}
+
+int32_t sh_event_record(uint64_t event, uint64_t stream) {
+    SH_CUDA(cudaEventRecord(as_event(event), as_stream(stream)), "cudaEventRecord");
+    return SH_OK;
+}
+
+int32_t sh_event_query(uint64_t event) {
+    const cudaError_t q = cudaEventQuery(as_event(event));
+    if (q == cudaSuccess) return SH_OK;
+    if (q == cudaErrorNotReady) return SH_ERR_BUSY;
+    return cuda_fail(q, "cudaEventQuery");
+}
+
+int32_t sh_event_wait(uint64_t event, int32_t timeout_ms) { return wait_event_bounded(as_event(event), timeout_ms); }
+
+int32_t sh_event_elapsed_ms(uint64_t start, uint64_t stop, float* ms_out) {
+    if (ms_out == nullptr) return fail(SH_ERR_INVALID_ARG, "null ms_out");
+    SH_CUDA(cudaEventElapsedTime(ms_out, as_event(start), as_event(stop)), "cudaEventElapsedTime");
+    return SH_OK;
+}
+
+// ── memory ──────────────────────────────────────────────────────────────
+
+int32_t sh_host_alloc(size_t bytes, void** ptr_out) {
+    if (ptr_out == nullptr || bytes == 0) return fail(SH_ERR_INVALID_ARG, "bad host allocation request");
+    SH_CUDA(cudaHostAlloc(ptr_out, bytes, cudaHostAllocPortable), "cudaHostAlloc");
+    return SH_OK;
+}
+
+int32_t sh_host_free(void* ptr) {
+    if (ptr == nullptr) return SH_OK;
+    SH_CUDA(cudaFreeHost(ptr), "cudaFreeHost");
+    return SH_OK;
+}
+
+int32_t sh_host_register(void* ptr, size_t bytes) {
+    if (ptr == nullptr || bytes == 0) return fail(SH_ERR_INVALID_ARG, "bad host registration request");
+    SH_CUDA(cudaHostRegister(ptr, bytes, cudaHostRegisterPortable), "cudaHostRegister");
+    return SH_OK;
+}
+
+int32_t sh_host_unregister(void* ptr) {
+    SH_CUDA(cudaHostUnregister(ptr), "cudaHostUnregister");
+    return SH_OK;
+}
+
+int32_t sh_device_alloc(size_t bytes, void** ptr_out) {
+    if (ptr_out == nullptr || bytes == 0) return fail(SH_ERR_INVALID_ARG, "bad device allocation request");
+    SH_CUDA(cudaMalloc(ptr_out, bytes), "cudaMalloc");
+    return SH_OK;
+}
+
+int32_t sh_device_free(void* ptr) {
+    if (ptr == nullptr) return SH_OK;
+    SH_CUDA(cudaFree(ptr), "cudaFree");
+    return SH_OK;
+}
+
+int32_t sh_pack_rows(void* dst, int64_t dst_ld, const void* src, int64_t src_ld, int64_t rows, int64_t row_bytes,
+                     int32_t n_threads) {
+    if (dst == nullptr || src == nullptr || rows < 0 || row_bytes < 0 || dst_ld < row_bytes || src_ld < row_bytes)
+        return fail(SH_ERR_INVALID_ARG, "bad pack_rows arguments");
+    if (rows == 0 || row_bytes == 0) return SH_OK;
+    auto work = [=](int64_t r0, int64_t r1) {
+        uint8_t* d = static_cast<uint8_t*>(dst);
+        const uint8_t* s = static_cast<const uint8_t*>(src);
+        if (dst_ld == row_bytes && src_ld == row_bytes) {
+            memcpy(d + r0 * row_bytes, s + r0 * row_bytes, static_cast<size_t>((r1 - r0) * row_bytes));
+            return;
+        }
+        for (int64_t r = r0; r < r1; ++r) memcpy(d + r * dst_ld, s + r * src_ld, static_cast<size_t>(row_bytes));
+    };
+    const int64_t total = rows * row_bytes;
+    int threads = std::max(1, static_cast<int>(n_threads));
+    threads = static_cast<int>(std::min<int64_t>(threads, std::max<int64_t>(1, total / (4 << 20))));
+    threads = static_cast<int>(std::min<int64_t>(threads, rows));
+    if (threads <= 1) {
+        work(0, rows);
+        return SH_OK;
+    }
+    std::vector<std::thread> pool;
+    pool.reserve(static_cast<size_t>(threads));
+    const int64_t chunk = (rows + threads - 1) / threads;
+    for (int t = 0; t < threads; ++t) {
+        const int64_t r0 = t * chunk, r1 = std::min(rows, r0 + chunk);
+        if (r0 >= r1) break;
+        pool.emplace_back(work, r0, r1);
+    }
+    for (auto& th : pool) th.join();
+    return SH_OK;
+}
+
+// ── data movement ───────────────────────────────────────────────────────
+
+int32_t sh_copy_h2d_async(void* dst_dev, const void* src_host, size_t bytes, uint64_t stream) {
+    if (bytes == 0) return SH_OK;
+    if (dst_dev == nullptr || src_host == nullptr) return fail(SH_ERR_INVALID_ARG, "null copy pointer");
+    SH_CUDA(cudaMemcpyAsync(dst_dev, src_host, bytes, cudaMemcpyHostToDevice, as_stream(stream)), "cudaMemcpyAsync H2D");
+    g_ctr.h2d_copies.fetch_add(1, std::memory_order_relaxed);
+    g_ctr.h2d_bytes.fetch_add(static_cast<int64_t>(bytes), std::memory_order_relaxed);
+    return SH_OK;
+}
+
+int32_t sh_pull_block_async(void* dst_local, const void* src_dev, size_t bytes, uint64_t stream) {
+    if (bytes == 0) return SH_OK;
+    if (dst_local == nullptr || src_dev == nullptr) return fail(SH_ERR_INVALID_ARG, "null copy pointer");
+    SH_CUDA(cudaMemcpyAsync(dst_local, src_dev, bytes, cudaMemcpyDeviceToDevice, as_stream(stream)),
+            "cudaMemcpyAsync D2D");
+    g_ctr.peer_copies.fetch_add(1, std::memory_order_relaxed);
+    g_ctr.peer_bytes.fetch_add(static_cast<int64_t>(bytes), std::memory_order_relaxed);
+    return SH_OK;
+}
+
+int32_t sh_peer_enable(int32_t peer_device) {
+    int cur = 0;
+    SH_CUDA(cudaGetDevice(&cur), "cudaGetDevice");
+    if (cur == peer_device) return SH_OK;
+    int can = 0;
+    SH_CUDA(cudaDeviceCanAccessPeer(&can, cur, peer_device), "cudaDeviceCanAccessPeer");
+    if (!can) return fail(SH_ERR_UNSUPPORTED, "device %d cannot access device %d", cur, peer_device);
+    const cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
+    if (e == cudaErrorPeerAccessAlreadyEnabled) {
+        (void)cudaGetLastError();
+        return SH_OK;
+    }
+    if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceEnablePeerAccess");
+    return SH_OK;
+}
+
+int32_t sh_ipc_export(void* dev_ptr, uint8_t handle_out[64]) {
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    if (dev_ptr == nullptr || handle_out == nullptr) return fail(SH_ERR_INVALID_ARG, "null ipc argument");
+    cudaIpcMemHandle_t h;
+    SH_CUDA(cudaIpcGetMemHandle(&h, dev_ptr), "cudaIpcGetMemHandle");
+    memcpy(handle_out, &h, 64);
+    return SH_OK;
+}
+
+int32_t sh_ipc_open(const uint8_t handle[64], void** dev_ptr_out) {
+    if (handle == nullptr || dev_ptr_out == nullptr) return fail(SH_ERR_INVALID_ARG, "null ipc argument");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, 64);
+    SH_CUDA(cudaIpcOpenMemHandle(dev_ptr_out, h, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle");
+    return SH_OK;
+}
+
+int32_t sh_ipc_close(void* dev_ptr) {
+    if (dev_ptr == nullptr) return SH_OK;
+    SH_CUDA(cudaIpcCloseMemHandle(dev_ptr), "cudaIpcCloseMemHandle");
+    return SH_OK;
+}
+
+// ── the block kernel ────────────────────────────────────────────────────
+
+int32_t sh_dequant_block_async(const ShParamDesc* descs, int32_t n_descs, const void* packed_dev, size_t packed_bytes,
+                               void* out_dev, size_t out_bytes, int32_t out_dtype, uint64_t stream,
+                               int32_t* status_dev) {
+    return launch_block(descs, n_descs, packed_dev, packed_bytes, out_dev, out_bytes, out_dtype, as_stream(stream),
+                        status_dev);
+}
+
+int32_t sh_stream_block_async(const ShParamDesc* descs, int32_t n_descs, const void* packed_host, size_t packed_bytes,
+                              void* staging_dev, void* out_dev, size_t out_bytes, int32_t out_dtype,
+                              uint64_t copy_stream, uint64_t dequant_stream, uint64_t ev_copied, uint64_t ev_ready,
+                              int32_t* status_dev) {
+    if (packed_host == nullptr || staging_dev == nullptr) return fail(SH_ERR_INVALID_ARG, "null image pointer");
+    if (copy_stream != dequant_stream && ev_copied == 0)
+        return fail(SH_ERR_INVALID_ARG, "two streams need ev_copied to order the kernel after the copy");
+    // validate before anything is enqueued so a bad descriptor leaves both streams untouched
+    {
+        const int max_plans = (std::max(n_descs, 1) + sq::kMaxDescs - 1) / sq::kMaxDescs;
+        std::vector<sq::BlockPlan> plans(static_cast<size_t>(max_plans));
+        int n_plans = 0;
+        char err[256];
+        if (n_descs < 0 || (n_descs > 0 && descs == nullptr)) return fail(SH_ERR_INVALID_ARG, "null descriptor array");
+        const int rc = sq::build_plans(descs, n_descs, staging_dev, packed_bytes, out_dev, out_bytes, out_dtype,
+                                       plans.data(), &n_plans, nullptr, nullptr, err, sizeof(err));
+        if (rc != SH_OK) return fail(rc, "%s", err);
+    }
+    int rc = sh_copy_h2d_async(staging_dev, packed_host, packed_bytes, copy_stream);
+    if (rc != SH_OK) return rc;
+    if (ev_copied != 0) {
+        SH_CUDA(cudaEventRecord(as_event(ev_copied), as_stream(copy_stream)), "cudaEventRecord");
+        if (copy_stream != dequant_stream)
+            SH_CUDA(cudaStreamWaitEvent(as_stream(dequant_stream), as_event(ev_copied), 0), "cudaStreamWaitEvent");
+    }
+    rc = launch_block(descs, n_descs, staging_dev, packed_bytes, out_dev, out_bytes, out_dtype,
+                      as_stream(dequant_stream), status_dev);
+    if (rc != SH_OK) return rc;
+    if (ev_ready != 0) SH_CUDA(cudaEventRecord(as_event(ev_ready), as_stream(dequant_stream)), "cudaEventRecord");
+    return SH_OK;
+}
+
+int32_t sh_profile_enable(int32_t on) {
+    g_prof_on.store(on ? 1 : 0);
+    return SH_OK;
+}
+
+int32_t sh_profile_collect(double* kernel_ms_out, int64_t* launches_out, int64_t* elements_out, int64_t* bytes_out,
+                           int32_t timeout_ms) {
+    std::vector<ProfRecord> recs;
+    {
+        std::lock_guard<std::mutex> lk(g_prof_mu);
+        recs.swap(g_prof_pending);
+    }
+    double ms = 0.0;
+    int64_t elements = 0, bytes = 0, n = 0;
+    int rc = SH_OK;
+    for (auto& r : recs) {
+        if (rc == SH_OK) rc = wait_event_bounded(r.stop, timeout_ms);
+        if (rc == SH_OK) {
+            float t = 0.f;
+            if (cudaEventElapsedTime(&t, r.start, r.stop) == cudaSuccess) {
+                ms += t;
+                elements += r.elements;
+                bytes += r.bytes;
+                ++n;
+            }
+        }
+    }
+    {
+        std::lock_guard<std::mutex> lk(g_prof_mu);
+        for (auto& r : recs) {
+            g_prof_free.push_back(r.start);
+            g_prof_free.push_back(r.stop);
+        }
+    }
+    if (kernel_ms_out) *kernel_ms_out = ms;
+    if (launches_out) *launches_out = n;
+    if (elements_out) *elements_out = elements;
+    if (bytes_out) *bytes_out = bytes;
+    return rc;
+}
+
+}  // extern "C"

@@ -1,0 +1,118 @@
+"""VRAM slabs for the INT8 streaming path.
+
+The reference allocates a fresh ``torch.empty`` for every block load
+(``src/stagehand/scheduler.py:936-941``) and frees it on eviction, which churns
+the caching allocator.  Here evicted slabs go back to a free list and are reused
+by the next load of a block of the same size.  Slabs are still ``torch`` tensors,
+so ``torch.cuda.memory_allocated()`` -- what the watermarks read -- sees them;
+bytes parked in the free list are reported through :meth:`reusable_bytes` so the
+budget manager can treat them as free.
+
+Reuse is stream-safe: a slab carries the event recorded on the stream that last
+read it, and the next writer's stream waits for that event (device-side; the host
+never blocks).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any
+
+import torch
+
+__all__ = ["DeviceSlab", "DeviceSlabPool", "StagingRing"]
+
+
+@dataclass
+class DeviceSlab:
+    tensor: torch.Tensor              # uint8 on the device
+    nbytes: int
+    last_use: Any = None              # events.Event recorded after the last reader / writer was queued
+    slab_id: int = -1
+
+
+class DeviceSlabPool:
+    """Exact-size free lists of output slabs (one list per distinct block size)."""
+
+    def __init__(self, device: torch.device | str = "cuda", max_parked_bytes: int | None = None) -> None:
+        self._device = torch.device(device)
+        self._free: dict[int, list[DeviceSlab]] = {}
+        self._parked_bytes = 0
+        self._max_parked = max_parked_bytes
+        self._next_id = 0
+        self.allocations = 0
+        self.reuses = 0
+
+    def acquire(self, nbytes: int) -> DeviceSlab:
+        """A slab of exactly *nbytes*: a parked one if there is any, else a new allocation."""
+        bucket = self._free.get(nbytes)
+        if bucket:
+            slab = bucket.pop()
+            self._parked_bytes -= slab.nbytes
+            self.reuses += 1
+            return slab
+        try:
+            tensor = torch.empty(nbytes, dtype=torch.uint8, device=self._device)
+        except torch.OutOfMemoryError:
+            self.trim()
+            tensor = torch.empty(nbytes, dtype=torch.uint8, device=self._device)
+        self.allocations += 1
+        self._next_id += 1
+        slab = DeviceSlab(tensor=tensor, nbytes=nbytes, slab_id=self._next_id)
+        if self._device.type == "cuda":
+            # The caching allocator may hand back memory that kernels already queued on the
+            # allocating stream still use; the slab's first writer (another stream) waits for them.
+            from stagehand_b200.events import acquire_event
+
+            slab.last_use = acquire_event().record(torch.cuda.current_stream(self._device))
+        return slab
+
+    def release(self, slab: DeviceSlab, stream: torch.cuda.Stream | None = None) -> None:
+        """Park *slab*; readers queued on *stream* (default: current) finish before its next writer starts."""
+        if self._device.type == "cuda":
+            from stagehand_b200.events import acquire_event, release_event
+
+            release_event(slab.last_use)
+            slab.last_use = acquire_event().record(
+                stream if stream is not None else torch.cuda.current_stream(self._device))
+        if self._max_parked is not None and self._parked_bytes + slab.nbytes > self._max_parked:
+            return   # dropped: the tensor goes back to the caching allocator
+        self._free.setdefault(slab.nbytes, []).append(slab)
+        self._parked_bytes += slab.nbytes
+
+    def reusable_bytes(self) -> int:
+        return self._parked_bytes
+
+    def trim(self) -> None:
+        """Give every parked slab back to the allocator."""
+        self._free.clear()
+        self._parked_bytes = 0
+
+
+class StagingRing:
+    """A small ring of INT8 staging slabs: where packed images land before they are expanded.
+
+    ``next()`` hands out slabs round-robin.  The caller makes its copy stream wait
+    on ``slab.last_use`` (the event recorded after the kernel that last read the
+    slab) so a copy never overwrites an image that is still being expanded.
+    """
+
+    def __init__(self, n_slabs: int, slab_bytes: int, device: torch.device | str = "cuda") -> None:
+        if n_slabs < 1:
+            raise ValueError("the staging ring needs at least one slab")
+        self._slabs = [
+            DeviceSlab(tensor=torch.empty(slab_bytes, dtype=torch.uint8, device=device), nbytes=slab_bytes, slab_id=i)
+            for i in range(n_slabs)
+        ]
+        self._cursor = 0
+        self.slab_bytes = slab_bytes
+
+    def __len__(self) -> int:
+        return len(self._slabs)
+
+    def next(self) -> DeviceSlab:
+        slab = self._slabs[self._cursor]
+        self._cursor = (self._cursor + 1) % len(self._slabs)
+        return slab
+
+    def total_bytes(self) -> int:
+        return self.slab_bytes * len(self._slabs)

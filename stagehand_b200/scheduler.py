@@ -1,0 +1,755 @@
+"""Block scheduler: k-lookahead prefetch, watermark eviction, and the load paths.
+
+Public surface and bookkeeping follow the reference scheduler
+(``src/stagehand/scheduler.py``): ``StaticLookaheadPolicy`` (``:65-142``),
+``before_block`` / ``after_block`` (``:773-850``), ``_prefetch_ahead`` (``:854-883``),
+``_load_block_to_gpu`` (``:885-951``), ``_finalize_gpu_load`` (``:1090-1124``),
+``_run_eviction`` / ``_evict_block`` (``:1128-1375``).
+
+What differs is *how a SquareQ-backed block reaches VRAM*.  The reference
+dequantises INT8 to the runtime dtype on the calling thread and DMAs the result
+(``:243-325``, ``:953-987``).  Here the block's packed INT8 image (built once, kept
+in page-locked memory) is copied on the copy stream and expanded by the sm_100a
+block kernel on the dequant stream into a pooled VRAM slab; ``before_block`` makes
+the compute stream wait on the block's ready event instead of blocking the host.
+There is no CPU fallback for that path: without CUDA and the native library a
+SquareQ load raises :class:`TransferError`.
+
+Module-backed and safetensors-backed blocks keep the reference's torch-copy paths.
+"""
+from __future__ import annotations
+
+import logging
+import mmap
+import os
+import time
+from pathlib import Path
+from typing import TYPE_CHECKING, Any, Protocol
+
+import torch
+from torch import nn
+
+from stagehand_b200.errors import StagehandOOMError, TransferError
+from stagehand_b200.residency import BlockState
+
+if TYPE_CHECKING:
+    from stagehand_b200.config import StagehandConfig
+    from stagehand_b200.packed import PackedBlockImage
+    from stagehand_b200.pool import PinnedSlab
+    from stagehand_b200.registry import BlockEntry, BlockRegistry, FileParamSpec
+    from stagehand_b200.residency import ResidencyEntry, ResidencyMap
+    from stagehand_b200.streamer import HostImage, StreamTicket
+    from stagehand_b200.telemetry import StagehandTelemetry
+    from stagehand_b200.transfer import AsyncTransferEngine, TransferHandle
+
+__all__ = ["StaticLookaheadPolicy", "StagehandScheduler"]
+
+log = logging.getLogger(__name__)
+_STALL_LOGS = str(os.getenv("SERENITY_STAGEHAND_STALL_LOGS", "0")).strip().lower() in {"1", "true", "yes", "on"}
+
+Layout = list[tuple[str, tuple[int, ...], torch.dtype, int, int]]
+
+
+class BudgetLike(Protocol):
+    def above_high_watermark(self) -> bool: ...
+    def below_low_watermark(self) -> bool: ...
+
+
+class GuardsLike(Protocol):
+    def check_output(self, tensor: torch.Tensor, block_id: str, step: int) -> tuple[int, int]: ...
+
+
+class StaticLookaheadPolicy:
+    """Prefetch the next ``prefetch_window`` blocks; evict by ``distance to next use x size``."""
+
+    def __init__(self, prefetch_window: int = 3, eviction_cooldown_steps: int = 2) -> None:
+        self.prefetch_window = prefetch_window
+        self.eviction_cooldown_steps = eviction_cooldown_steps
+
+    def blocks_to_prefetch(self, cursor: int, total_blocks: int, residency_states: dict[str, str]) -> list[int]:
+        """Execution-order indices ``cursor+1 .. cursor+prefetch_window`` that exist."""
+        return [i for i in range(cursor + 1, cursor + 1 + self.prefetch_window) if i < total_blocks]
+
+    def score_for_eviction(self, block_id: str, current_cursor: int, entry_exec_order: int, total_blocks: int,
+                           size_bytes: int) -> float:
+        distance = (entry_exec_order - current_cursor) % total_blocks
+        if distance == 0:
+            distance = total_blocks   # the block at the cursor is used again a full pass from now
+        return float(distance * size_bytes)
+
+    def should_evict(self, last_used_step: int, current_step: int) -> bool:
+        return current_step - last_used_step > self.eviction_cooldown_steps
+
+
+# ── parameter <-> flat buffer helpers ────────────────────────────────────
+
+
+def _build_param_layout(module: nn.Module, dtype: torch.dtype) -> Layout:
+    """``(name, shape, dtype, offset_bytes, numel)`` rows, cumulative and unpadded, in ``named_parameters()`` order."""
+    layout: Layout = []
+    offset = 0
+    for name, param in module.named_parameters():
+        layout.append((name, tuple(param.shape), dtype, offset, param.numel()))
+        offset += param.numel() * dtype.itemsize
+    return layout
+
+
+def _resolve(module: nn.Module, dotted: str) -> tuple[nn.Module, str]:
+    *path, leaf = dotted.split(".")
+    node = module
+    for part in path:
+        node = getattr(node, part)
+    return node, leaf
+
+
+def _get_param_data(module: nn.Module, dotted_name: str) -> torch.Tensor:
+    owner, leaf = _resolve(module, dotted_name)
+    return getattr(owner, leaf).data
+
+
+def _set_param_data(module: nn.Module, dotted_name: str, data: torch.Tensor) -> None:
+    """``param.data = data``; a parameter that cannot take it (e.g. a meta tensor) is replaced."""
+    owner, leaf = _resolve(module, dotted_name)
+    param = getattr(owner, leaf)
+    try:
+        param.data = data
+    except RuntimeError:
+        setattr(owner, leaf, nn.Parameter(data, requires_grad=param.requires_grad))
+
+
+def _restore_params_from_tensor(module: nn.Module, flat_bytes: torch.Tensor, layout: Layout) -> None:
+    """Point every parameter at its view inside the flat uint8 buffer."""
+    for name, shape, dtype, offset, numel in layout:
+        view = flat_bytes[offset : offset + numel * dtype.itemsize].view(dtype).reshape(shape)
+        _set_param_data(module, name, view)
+
+
+def _flatten_params_into_buffer(module: nn.Module, buffer: torch.Tensor, layout: Layout) -> None:
+    live = dict(module.named_parameters())
+    for name, _shape, dtype, offset, numel in layout:
+        buffer[offset : offset + numel * dtype.itemsize].view(dtype).copy_(live[name].data.to(dtype).reshape(-1))
+
+
+def _detach_params(module: nn.Module, layout: Layout) -> None:
+    """Empty every parameter so no view keeps the block's VRAM slab alive."""
+    for name, _shape, dtype, _offset, _numel in layout:
+        _set_param_data(module, name, torch.empty(0, dtype=dtype))
+
+
+class StagehandScheduler:
+    def __init__(self, registry: "BlockRegistry", residency: "ResidencyMap", transfer_engine: "AsyncTransferEngine",
+                 budget: BudgetLike, policy: StaticLookaheadPolicy, guards: GuardsLike | None,
+                 telemetry: "StagehandTelemetry", config: "StagehandConfig", inference_mode: bool = False) -> None:
+        self._registry = registry
+        self._residency = residency
+        self._engine = transfer_engine
+        self._budget = budget
+        self._policy = policy
+        self._guards = guards
+        self._telemetry = telemetry
+        self._config = config
+        self._inference_mode = inference_mode
+
+        self._current_step = 0
+        self._cursor = 0
+        self._backward_phase = False
+        self._defer_backward_eviction = False
+
+        self._ordered_blocks: list["BlockEntry"] = []
+        self._total_blocks = 0
+        self._order_to_id: dict[int, str] = {}
+        self.refresh_registry_snapshot()
+
+        self._pending_handles: dict[str, Any] = {}            # block_id -> TransferHandle | StreamTicket
+        # optional Serenity adapters: accepted and stored, as in the reference, but never required
+        self._conductor_adapter: Any = None
+        self._squareq_adapter: Any = None
+        self._eriquant_adapter: Any = None
+
+        self._file_maps: dict[str, tuple[Any, mmap.mmap, memoryview]] = {}
+        self._file_tensor_views: dict[tuple, torch.Tensor] = {}
+        self._squareq_layers: dict[str, dict[str, Any]] = {}
+        self._module_param_caches: dict[str, dict[str, torch.Tensor]] = {}
+
+        # INT8 path state (created on first SquareQ load)
+        self._streamer: Any = None
+        self._device_pool: Any = None
+        self._image_store: Any = None
+        self._image_plans: dict[str, "PackedBlockImage"] = {}
+        self._device_sources: dict[str, tuple[int, bool]] = {}      # block_id -> (device ptr of static section, is_peer)
+        self._device_source_fused = True
+        self._deferred_slabs: list[tuple[Any, "PinnedSlab"]] = []   # (copied event, pool slab) awaiting DMA completion
+        self._squareq_v2_loader: Any = None
+
+    # ── step lifecycle ───────────────────────────────────────────────
+
+    def refresh_registry_snapshot(self) -> None:
+        self._ordered_blocks = self._registry.blocks_in_order()
+        self._total_blocks = len(self._ordered_blocks)
+        self._order_to_id = {e.exec_order: e.block_id for e in self._ordered_blocks}
+        if getattr(self, "_image_plans", None):
+            self._image_plans.clear()
+
+    def begin_step(self, step: int) -> None:
+        self._current_step = step
+        self._cursor = 0
+        self._backward_phase = False
+        self._telemetry.begin_step(step)
+
+    def end_step(self) -> None:
+        self._backward_phase = False
+        self._engine.reap()
+        self._reap_deferred_slabs()
+        self._reconcile_file_backed_grads()
+        self._telemetry.end_step()
+
+    def enter_backward_phase(self) -> None:
+        self._backward_phase = True
+
+    def exit_backward_phase(self) -> None:
+        self._backward_phase = False
+
+    def set_defer_backward_eviction(self, enabled: bool) -> None:
+        self._defer_backward_eviction = enabled
+
+    def set_conductor_adapter(self, adapter: Any) -> None:
+        self._conductor_adapter = adapter
+
+    def set_squareq_adapter(self, adapter: Any) -> None:
+        self._squareq_adapter = adapter
+
+    def set_eriquant_adapter(self, adapter: Any) -> None:
+        self._eriquant_adapter = adapter
+
+    def set_squareq_v2_loader(self, loader: Any) -> None:
+        """Callable ``(safetensors_path, manifest_path) -> {layer: {qweight, scale, zero_point, bias}}``.
+
+        The reference imports this from a package that is not part of it
+        (``scheduler.py:631-649``); any loader with that return shape can be plugged in here.
+        """
+        self._squareq_v2_loader = loader
+
+    def _reconcile_file_backed_grads(self) -> None:
+        """Mutable parameters that live on the CPU get their gradients back on the CPU at step end."""
+        for entry in self._ordered_blocks:
+            if not entry.file_backed or not entry.module_param_names:
+                continue
+            module = entry.module_ref()
+            if module is None:
+                continue
+            mutable = set(entry.module_param_names)
+            for name, param in module.named_parameters():
+                if name in mutable and param.device.type == "cpu" and param.grad is not None \
+                        and param.grad.device.type != "cpu":
+                    param.grad = param.grad.to("cpu", non_blocking=True)
+
+    # ── sources ──────────────────────────────────────────────────────
+
+    def _get_file_view(self, source_path: str) -> memoryview:
+        key = str(Path(source_path).expanduser())
+        hit = self._file_maps.get(key)
+        if hit is None:
+            fh = Path(key).open("rb")
+            mm = mmap.mmap(fh.fileno(), length=0, access=mmap.ACCESS_READ)
+            hit = (fh, mm, memoryview(mm))
+            self._file_maps[key] = hit
+        return hit[2]
+
+    def _get_file_tensor_view(self, source_path: str, spec: "FileParamSpec") -> torch.Tensor:
+        path = str(Path(source_path).expanduser())
+        key = (path, int(spec.file_offset), int(spec.source_nbytes), spec.source_dtype, spec.source_shape)
+        view = self._file_tensor_views.get(key)
+        if view is None:
+            raw = self._get_file_view(path)[int(spec.file_offset) : int(spec.file_offset) + int(spec.source_nbytes)]
+            view = torch.frombuffer(raw, dtype=spec.source_dtype).reshape(spec.source_shape)
+            self._file_tensor_views[key] = view
+        return view
+
+    def _get_squareq_layers(self, source_path: str) -> dict[str, Any]:
+        """``payload["layers"]`` of a BP8 ``.fpk`` slab, memory-mapped and cached per path."""
+        from stagehand_b200.registry import _torch_load_lazy
+
+        key = str(Path(source_path).expanduser())
+        layers = self._squareq_layers.get(key)
+        if layers is None:
+            payload = _torch_load_lazy(Path(key))
+            if not isinstance(payload, dict):
+                raise ValueError(f"Invalid SquareQ slab payload at {key}")
+            layers = payload.get("layers")
+            if not isinstance(layers, dict):
+                raise ValueError(f"SquareQ slab missing 'layers' map at {key}")
+            self._squareq_layers[key] = layers
+        return layers
+
+    def _get_squareq_v2_layers(self, source_path: str) -> dict[str, Any]:
+        key = str(Path(source_path).expanduser())
+        layers = self._squareq_layers.get(key)
+        if layers is None:
+            manifest = str(Path(key).with_suffix(".manifest.json"))
+            loader = self._squareq_v2_loader
+            if loader is None:
+                from serenity.squareq.stagehand import get_squareq_v2_layers as loader  # same import as the reference
+            layers = loader(key, manifest)
+            self._squareq_layers[key] = layers
+        return layers
+
+    def close(self) -> None:
+        """Release file maps, cached slabs layers, packed images and the INT8 path's device objects."""
+        if self._streamer is not None:
+            try:
+                self._streamer.drain()
+            except TransferError:
+                log.warning("streams did not drain at close", exc_info=True)
+        self._reap_deferred_slabs(force=True)
+        if self._image_store is not None:
+            self._image_store.close()
+            self._image_store = None
+        if self._device_pool is not None:
+            self._device_pool.trim()
+        self._image_plans.clear()
+        self._file_tensor_views.clear()
+        for fh, mm, view in self._file_maps.values():
+            for closer in (view.release, mm.close, fh.close):
+                try:
+                    closer()
+                except Exception:
+                    pass
+        self._file_maps.clear()
+        self._squareq_layers.clear()
+        self._module_param_caches.clear()
+
+    # ── per-block hooks ──────────────────────────────────────────────
+
+    def before_block(self, block_id: str) -> None:
+        """Make *block_id* resident before it computes, then prefetch ahead."""
+        state = self._residency.get_state(block_id)
+        if state is BlockState.GPU_READY:
+            self._telemetry.record_prefetch_hit()
+        else:
+            t0 = time.monotonic()
+            was_in_flight = state is BlockState.PREFETCHING
+            if not was_in_flight:
+                self._load_block_to_gpu(block_id)
+            landed = False
+            if self._residency.get_state(block_id) is BlockState.PREFETCHING:
+                landed = self._await_pending(block_id)
+                self._finalize_gpu_load(block_id)
+            stall_ms = (time.monotonic() - t0) * 1e3
+            if was_in_flight and landed:
+                self._telemetry.record_soft_hit()        # prefetched and complete: nothing waited
+            else:
+                self._telemetry.record_stall(stall_ms)
+                self._telemetry.record_prefetch_miss()
+                if _STALL_LOGS and not was_in_flight:
+                    log.warning("Hard stall on block %s (was %s): %.2f ms", block_id, state.value, stall_ms)
+
+        self._residency.increment_ref(block_id)
+        self._residency.get_entry(block_id).last_used_step = self._current_step
+        self._cursor += 1
+
+        if self._budget.above_high_watermark():
+            self._run_eviction(ignore_cooldown=True)
+        self._prefetch_ahead()
+        if self._budget.above_high_watermark():
+            self._run_eviction(ignore_cooldown=True)
+
+    def after_block(self, block_id: str, output: torch.Tensor | None = None) -> None:
+        self._residency.decrement_ref(block_id)
+        self._residency.get_entry(block_id).last_used_step = self._current_step
+        if self._guards is not None and output is not None and self._config.nan_inf_check:
+            nans, infs = self._guards.check_output(output, block_id, self._current_step)
+            if nans or infs:
+                self._telemetry.record_nan_inf(nans, infs)
+        if self._budget.above_high_watermark() and not (self._backward_phase and self._defer_backward_eviction):
+            self._run_eviction(ignore_cooldown=True)
+
+    def _await_pending(self, block_id: str) -> bool:
+        """Order the caller's stream after the block's transfer.  Returns True when it had already finished."""
+        pending = self._pending_handles.pop(block_id, None)
+        if pending is None:
+            return True
+        if hasattr(pending, "ready"):                       # StreamTicket (INT8 path): device-side wait only
+            from stagehand_b200.events import release_event
+
+            done = pending.ready.done()
+            pending.ready.block_stream(torch.cuda.current_stream())
+            release_event(pending.ready)
+            if pending.host_slab is not None:
+                self._deferred_slabs.append((pending.copied, pending.host_slab))
+            else:
+                release_event(pending.copied)
+            return done
+        done = self._engine.poll(pending)
+        if not done:
+            self._engine.wait(pending)
+        return done
+
+    # ── prefetch ─────────────────────────────────────────────────────
+
+    def _prefetch_ahead(self) -> None:
+        states = {e.block_id: self._residency.get_state(e.block_id).value for e in self._ordered_blocks}
+        for idx in self._policy.blocks_to_prefetch(self._cursor - 1, self._total_blocks, states):
+            if idx >= self._total_blocks:
+                break
+            block_id = self._ordered_blocks[idx].block_id
+            if self._residency.get_state(block_id) in (BlockState.GPU_READY, BlockState.PREFETCHING):
+                continue
+            if not self._budget.can_prefetch():
+                break
+            self._load_block_to_gpu(block_id, speculative=True)
+
+    def _load_block_to_gpu(self, block_id: str, speculative: bool = False) -> None:
+        """Advance *block_id* towards GPU_READY (it ends PREFETCHING, or GPU_READY for module-backed blocks)."""
+        state = self._residency.get_state(block_id)
+        if state in (BlockState.GPU_READY, BlockState.PREFETCHING):
+            return
+        entry = self._registry.get(block_id)
+        res = self._residency.get_entry(block_id)
+
+        if entry.eriquant_backed:
+            raise TransferError(f"block {block_id!r} is eriquant-backed; that adapter path is not part of this runtime")
+
+        if not entry.file_backed and not entry.squareq_backed and state is BlockState.UNLOADED:
+            self._load_module_backed_direct(block_id, entry, res)
+            return
+
+        if entry.squareq_backed:
+            self._load_squareq_block(block_id, entry, res, state)
+            return
+
+        if state is BlockState.UNLOADED:
+            res.host_slab = self._stage_block_to_host(entry, res)
+            state = self._residency.get_state(block_id)
+        if state is BlockState.HOST_STAGED:
+            if res.gpu_tensor is None:
+                device = "cuda" if torch.cuda.is_available() else "cpu"
+                res.gpu_tensor = torch.empty(entry.size_bytes // entry.dtype.itemsize, dtype=entry.dtype, device=device)
+            self._pending_handles[block_id] = self._engine.submit_h2d(block_id, res.host_slab, res.gpu_tensor)
+            self._residency.transition(block_id, BlockState.PREFETCHING)
+            self._telemetry.record_h2d(entry.size_bytes)
+            self._telemetry.record_link(entry.size_bytes)
+
+    # ── SquareQ INT8 path ────────────────────────────────────────────
+
+    def _ensure_int8_path(self) -> None:
+        if self._streamer is not None:
+            return
+        if not torch.cuda.is_available():
+            raise TransferError(
+                "SquareQ-backed blocks are expanded by the sm_100a kernel; this process has no CUDA device "
+                "(there is no CPU fallback on this path)")
+        from stagehand_b200.device_pool import DeviceSlabPool
+        from stagehand_b200.streamer import ImageStore, Int8BlockStreamer
+
+        device = torch.device("cuda", torch.cuda.current_device())
+        n_staging = self._config.device_staging_slabs or (self._policy.prefetch_window + 1)
+        self._streamer = Int8BlockStreamer(device, self._engine.copy_stream, n_staging)
+        self._device_pool = DeviceSlabPool(device)
+        if hasattr(self._budget, "set_reusable_bytes_source"):
+            self._budget.set_reusable_bytes_source(self._device_pool.reusable_bytes)
+        self._image_store = ImageStore(self._image_cache_budget(), pinned=True)
+        # one staging ring sized for the largest image of the registry
+        largest = 0
+        largest_dyn = 0
+        for e in self._ordered_blocks:
+            if e.squareq_backed:
+                plan = self._image_plan(e)
+                largest = max(largest, plan.total_bytes)
+                largest_dyn = max(largest_dyn, plan.total_bytes - plan.static_bytes)
+        self._streamer.ensure_staging(largest, largest_dyn if self._device_sources else 0)
+
+    def _image_cache_budget(self) -> int:
+        mb = int(getattr(self._config, "packed_image_cache_mb", -1))
+        if mb >= 0:
+            return mb * 1024 * 1024
+        try:
+            import psutil
+
+            return int(psutil.virtual_memory().total // 2)
+        except Exception:
+            return 8 << 30
+
+    def _image_plan(self, entry: "BlockEntry") -> "PackedBlockImage":
+        plan = self._image_plans.get(entry.block_id)
+        if plan is None:
+            from stagehand_b200.packed import plan_block_image
+
+            source = str(entry.source_path)
+            layers = (self._get_squareq_v2_layers(source) if entry.source_format == "squareq_v2"
+                      else self._get_squareq_layers(source))
+            plan = plan_block_image(
+                entry.block_id, list(entry.param_layout), {s.param_name: s for s in entry.squareq_param_specs},
+                set(entry.module_param_names), layers, entry.module_ref(), entry.size_bytes)
+            self._image_plans[entry.block_id] = plan
+        return plan
+
+    def _stage_squareq_image(self, entry: "BlockEntry", plan: "PackedBlockImage") -> tuple["HostImage", Any]:
+        """Packed image of *entry* in page-locked memory: ``(image, pool slab or None)``.
+
+        Cached images cost nothing after the first load; when the cache budget is
+        spent the image is packed into a pool slab that goes back once its DMA is done.
+        """
+        from stagehand_b200.streamer import HostImage
+
+        module = entry.module_ref()
+        cache = self._module_param_caches.setdefault(entry.block_id, {})
+        image = self._image_store.get(entry.block_id) or self._image_store.create(entry.block_id, plan.total_bytes)
+        slab = None
+        if image is None:
+            self._reap_deferred_slabs()
+            pool = self._engine._pool
+            if plan.total_bytes > pool.slab_bytes:
+                raise StagehandOOMError(
+                    f"packed image of block {entry.block_id!r} ({plan.total_bytes} bytes) does not fit a pinned slab "
+                    f"({pool.slab_bytes} bytes) and the image cache is full; raise pinned_slab_mb or "
+                    "packed_image_cache_mb")
+            slab = pool.try_acquire(plan.total_bytes)
+            if slab is None:
+                self._reap_deferred_slabs(force=True)
+                slab = pool.acquire(plan.total_bytes)
+            image = HostImage(buffer=slab.buffer[: plan.total_bytes], nbytes=plan.total_bytes,
+                              pinned=torch.cuda.is_available())
+        else:
+            self._telemetry.record_image_cache_hit() if image.static_ready else None
+        if not image.static_ready:
+            plan.fill_static(image.buffer, threads=int(getattr(self._config, "pack_threads", 8)))
+            image.static_ready = True
+        if plan.dynamic_rows:
+            if image.last_copy is not None and not image.last_copy.done():
+                image.last_copy.wait(60_000)   # the previous DMA of this image still reads the dynamic section
+            plan.refresh_dynamic(image.buffer, module, cache)
+        return image, slab
+
+    def _load_squareq_block(self, block_id: str, entry: "BlockEntry", res: "ResidencyEntry", state: BlockState) -> None:
+        self._ensure_int8_path()
+        plan = self._image_plan(entry)
+        device_src = self._device_sources.get(block_id)
+        if state is BlockState.UNLOADED:
+            res.param_layout = list(entry.param_layout)
+            if device_src is None or plan.dynamic_rows:
+                image, slab = self._stage_squareq_image(entry, plan) if device_src is None else \
+                    self._stage_dynamic_only(entry, plan)
+                res.host_slab = (image, slab)
+            self._residency.transition(block_id, BlockState.HOST_STAGED)
+        image, slab = res.host_slab if res.host_slab is not None else (None, None)
+        out_slab = self._device_pool.acquire(entry.size_bytes)
+        if device_src is None:
+            ticket = self._streamer.submit_from_host(plan, image, out_slab)
+        else:
+            ticket = self._streamer.submit_from_device(plan, device_src[0], device_src[1], self._device_source_fused,
+                                                       image, out_slab)
+        ticket.host_slab = slab
+        res.host_slab = None
+        res.device_slab = out_slab
+        res.gpu_tensor = out_slab.tensor[: entry.size_bytes].view(entry.dtype)
+        self._pending_handles[block_id] = ticket
+        self._residency.transition(block_id, BlockState.PREFETCHING)
+        self._telemetry.record_h2d(entry.size_bytes)
+        self._telemetry.record_link(ticket.link_bytes)
+        self._telemetry.record_peer(ticket.peer_bytes)
+        self._telemetry.record_dequant_launch(ticket.launches)
+
+    def _stage_dynamic_only(self, entry: "BlockEntry", plan: "PackedBlockImage") -> tuple["HostImage", Any]:
+        """Host image that only carries the dynamic section (the static one is resident in HBM)."""
+        image = self._image_store.get(entry.block_id) or self._image_store.create(entry.block_id, plan.total_bytes)
+        if image is None:
+            raise StagehandOOMError(f"no pinned memory left for the dynamic section of block {entry.block_id!r}")
+        if image.last_copy is not None and not image.last_copy.done():
+            image.last_copy.wait(60_000)
+        plan.refresh_dynamic(image.buffer, entry.module_ref(), self._module_param_caches.setdefault(entry.block_id, {}))
+        return image, None
+
+    def set_device_sources(self, sources: dict[str, tuple[int, bool]], fused: bool = True) -> None:
+        """Declare blocks whose static INT8 image is resident in HBM: ``block_id -> (pointer, is_peer)``.
+
+        With *fused* the block kernel reads the image in place (plain loads over NVLink
+        for a peer); otherwise it is pulled into a local staging slab by a copy engine first.
+        """
+        self._device_sources = dict(sources)
+        self._device_source_fused = fused
+
+    def _reap_deferred_slabs(self, force: bool = False) -> None:
+        from stagehand_b200.events import release_event
+
+        keep = []
+        for copied, slab in self._deferred_slabs:
+            if copied is not None and not copied.done():
+                if not force:
+                    keep.append((copied, slab))
+                    continue
+                copied.wait(60_000)
+            release_event(copied)
+            self._engine._pool.release(slab)
+        self._deferred_slabs = keep
+
+    # ── generic (torch-copy) load paths ──────────────────────────────
+
+    def _stage_block_to_host(self, entry: "BlockEntry", res: "ResidencyEntry") -> "PinnedSlab":
+        """Fill a pinned slab with a module- or safetensors-backed block in the runtime dtype."""
+        if entry.squareq_backed:
+            raise TransferError("SquareQ-backed blocks are staged as packed INT8 images (see _load_squareq_block)")
+        slab = self._engine._pool.acquire(entry.size_bytes)
+        module = entry.module_ref()
+        res.param_layout = None
+        if isinstance(slab, list):
+            self._engine._pool.release(slab)
+            raise StagehandOOMError(
+                f"block {entry.block_id!r} ({entry.size_bytes} bytes) spans several pinned slabs; "
+                f"raise pinned_slab_mb above {entry.size_bytes / 2**20:.0f}")
+        if module is None:
+            slab.buffer[: entry.size_bytes].zero_()
+        elif entry.file_backed:
+            layout = list(entry.param_layout)
+            res.param_layout = layout
+            self._fill_from_files(entry, module, slab.buffer, layout)
+        elif any(True for _ in module.parameters()):
+            layout = _build_param_layout(module, entry.dtype)
+            res.param_layout = layout
+            _flatten_params_into_buffer(module, slab.buffer, layout)
+        else:
+            slab.buffer[: max(entry.size_bytes, 1)].zero_()
+        self._residency.transition(entry.block_id, BlockState.HOST_STAGED)
+        return slab
+
+    def _fill_from_files(self, entry: "BlockEntry", module: nn.Module, buffer: torch.Tensor, layout: Layout) -> None:
+        """safetensors-backed block: file regions (cast if needed) + live module-owned parameters, else zeros."""
+        specs = {s.param_name: s for s in entry.file_param_specs}
+        mutable = set(entry.module_param_names)
+        live = dict(module.named_parameters())
+        for name, _shape, dtype, offset, numel in layout:
+            region = buffer[offset : offset + numel * dtype.itemsize]
+            spec = specs.get(name)
+            if spec is not None:
+                path = spec.file_path or str(entry.source_path)
+                region.view(dtype).copy_(self._get_file_tensor_view(path, spec).reshape(-1))
+            elif name in mutable and name in live and live[name].data.numel() == numel:
+                region.view(dtype).copy_(live[name].data.to(dtype).reshape(-1))
+            else:
+                region.zero_()
+
+    def _load_module_backed_direct(self, block_id: str, entry: "BlockEntry", res: "ResidencyEntry") -> None:
+        """Module-backed block: parameters live on the module; copy them into one flat device tensor."""
+        module = entry.module_ref()
+        if module is None:
+            return   # as in the reference: a collected module is a silent no-op
+        device = "cuda" if torch.cuda.is_available() else "cpu"
+        layout = _build_param_layout(module, entry.dtype)
+        res.param_layout = layout
+        flat = torch.empty(entry.size_bytes // entry.dtype.itemsize, dtype=entry.dtype, device=device)
+        res.gpu_tensor = flat
+        flat_bytes = flat.view(torch.uint8)
+        live = dict(module.named_parameters())
+        for name, _shape, dtype, offset, numel in layout:
+            flat_bytes[offset : offset + numel * dtype.itemsize].view(dtype).copy_(
+                live[name].data.to(dtype).reshape(-1), non_blocking=True)
+        _restore_params_from_tensor(module, flat_bytes, layout)
+        for param in module.parameters():
+            if param.grad is not None and param.grad.device.type != device:
+                param.grad = param.grad.to(device, non_blocking=True)
+        for nxt in (BlockState.HOST_STAGED, BlockState.PREFETCHING, BlockState.GPU_READY):
+            self._residency.transition(block_id, nxt)
+        self._telemetry.record_h2d(entry.size_bytes)
+        self._telemetry.record_link(entry.size_bytes)
+
+    def _finalize_gpu_load(self, block_id: str) -> None:
+        """PREFETCHING -> GPU_READY: repoint the module's parameters at views of the block's flat tensor."""
+        self._residency.transition(block_id, BlockState.GPU_READY)
+        entry = self._registry.get(block_id)
+        res = self._residency.get_entry(block_id)
+        module = entry.module_ref()
+        if module is not None and res.param_layout is not None and res.gpu_tensor is not None:
+            _restore_params_from_tensor(module, res.gpu_tensor.view(torch.uint8), res.param_layout)
+            target = res.gpu_tensor.device
+            for param in module.parameters():
+                if param.grad is not None and param.grad.device != target:
+                    param.grad = param.grad.to(target, non_blocking=True)
+        if res.host_slab is not None and not isinstance(res.host_slab, tuple):
+            self._engine._pool.release(res.host_slab)
+        res.host_slab = None
+
+    # ── eviction ─────────────────────────────────────────────────────
+
+    def _run_eviction(self, ignore_cooldown: bool = False) -> None:
+        """Evict unreferenced blocks outside the prefetch window, best score first, until below the low watermark."""
+        cooldown = 0 if ignore_cooldown else self._policy.eviction_cooldown_steps
+        candidates = self._residency.eviction_candidates(self._current_step, cooldown)
+        window_start = max(self._cursor - 1, 0)
+        protected = {
+            self._ordered_blocks[i].block_id
+            for i in range(window_start + 1, window_start + 1 + self._policy.prefetch_window)
+            if i < self._total_blocks
+        }
+        ranked = []
+        for block_id, _res in candidates:
+            if block_id in protected:
+                continue
+            entry = self._registry.get(block_id)
+            ranked.append((self._policy.score_for_eviction(block_id, self._cursor, entry.exec_order,
+                                                           self._total_blocks, entry.size_bytes), block_id))
+        ranked.sort(reverse=True)
+        for _score, block_id in ranked:
+            if self._budget.below_low_watermark():
+                break
+            self._evict_block(block_id, save_back=not self._inference_mode)
+            self._telemetry.record_eviction()
+
+    def _release_device_storage(self, res: "ResidencyEntry") -> None:
+        res.gpu_tensor = None
+        if res.device_slab is not None:
+            self._device_pool.release(res.device_slab)   # event on the current stream guards its reuse
+            res.device_slab = None
+        if res.host_slab is not None and not isinstance(res.host_slab, tuple):
+            self._engine._pool.release(res.host_slab)
+        res.host_slab = None
+        res.param_layout = None
+
+    def _evict_block(self, block_id: str, save_back: bool = False) -> None:
+        """Drop *block_id* from VRAM.
+
+        Source-backed blocks (SquareQ, safetensors) are never copied back: frozen
+        parameters are emptied, module-owned ones are cloned off the slab -- to the
+        CPU, or kept on the GPU while backward eviction is deferred.  Module-backed
+        blocks move their parameters to standalone CPU tensors.
+        """
+        entry = self._registry.get(block_id)
+        res = self._residency.get_entry(block_id)
+        module = entry.module_ref()
+        source_backed = entry.file_backed or entry.squareq_backed
+        self._residency.transition(block_id, BlockState.EVICTING if save_back else BlockState.GPU_FREEING)
+
+        if module is not None and res.param_layout is not None:
+            if source_backed:
+                mutable = set(entry.module_param_names)
+                keep_on_gpu = self._defer_backward_eviction and not self._backward_phase
+                for name, _shape, dtype, _off, _numel in res.param_layout:
+                    if name in mutable:
+                        live = _get_param_data(module, name)
+                        target = live.device if keep_on_gpu else torch.device("cpu")
+                        _set_param_data(module, name, live.to(target).clone())
+                    elif (entry.file_param_specs and self._backward_phase and self._defer_backward_eviction
+                          and self._restore_cpu_file_view(entry, module, name, dtype)):
+                        pass
+                    else:
+                        _set_param_data(module, name, torch.empty(0, dtype=dtype))
+                if save_back:
+                    for name, param in module.named_parameters():
+                        if name in mutable and param.grad is not None and param.grad.device.type != "cpu":
+                            param.grad = param.grad.to("cpu", non_blocking=True)
+            else:
+                for name, _shape, _dtype, _off, _numel in res.param_layout:
+                    _set_param_data(module, name, _get_param_data(module, name).to("cpu").clone())
+                if save_back:
+                    for param in module.parameters():
+                        if param.grad is not None and param.grad.device.type != "cpu":
+                            param.grad = param.grad.to("cpu")
+        self._release_device_storage(res)
+        self._residency.transition(block_id, BlockState.UNLOADED)
+
+    def _restore_cpu_file_view(self, entry: "BlockEntry", module: nn.Module, name: str, dtype: torch.dtype) -> bool:
+        """During deferred backward eviction a frozen file-backed parameter becomes a CPU view of its file region."""
+        for spec in entry.file_param_specs:
+            if spec.param_name == name:
+                view = self._get_file_tensor_view(spec.file_path or str(entry.source_path), spec)
+                _set_param_data(module, name, view if spec.source_dtype == dtype else view.to(dtype))
+                return True
+        return False

@@ -1,0 +1,239 @@
+"""CPU tests of the host side: library exports, registry conversion, packed-image planning,
+residency / pool / policy bookkeeping.  No GPU compute is called."""
+from __future__ import annotations
+
+import ctypes
+import re
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+from torch import nn
+
+from conftest import GOLDEN, REPO_ROOT
+from desc_interp import expand
+import stagehand_b200 as sh
+from stagehand_b200 import _native
+from stagehand_b200.packed import plan_block_image
+from stagehand_b200.workloads import BLOCK_PATTERNS, TinyBlockModel, write_squareq_fpk
+
+
+def test_library_exports_every_declared_symbol() -> None:
+    header = (REPO_ROOT / "include" / "stagehand_b200.h").read_text()
+    declared = set(re.findall(r"^int32_t\s+(sh_\w+)\s*\(", header, flags=re.M))
+    assert declared == set(_native.EXPORTED_SYMBOLS)
+    lib = _native.lib()
+    for name in declared:
+        assert getattr(lib, name) is not None
+    assert lib.sh_abi_version() == 1
+    assert ctypes.sizeof(_native.ShParamDesc) == 64
+
+
+def test_public_names_match_the_reference_surface() -> None:
+    for name in ["StagehandConfig", "StagehandRuntime", "BlockEntry", "BlockRegistry", "SquareQParamSpec",
+                 "BlockState", "ResidencyEntry", "ResidencyMap", "AsyncTransferEngine", "TransferHandle",
+                 "StaticLookaheadPolicy", "StagehandScheduler", "BudgetManager", "NumericGuard", "PinnedPool",
+                 "PinnedSlab", "StagehandTelemetry", "StepMetrics", "LayerRuntime", "layer", "wrap", "Runtime",
+                 "DtypeMismatchError", "InvalidStateTransitionError", "StagehandError", "StagehandOOMError",
+                 "TransferError"]:
+        assert hasattr(sh, name), name
+    cfg = sh.StagehandConfig()
+    assert (cfg.pinned_pool_mb, cfg.pinned_slab_mb, cfg.prefetch_window_blocks) == (8192, 256, 3)
+
+
+def _tiny_fpk(tmp_path: Path, dtype=torch.float32):
+    model = nn.Module()
+    model.add_module("block_0", nn.Linear(8, 8, bias=True))
+    for p in model.parameters():
+        p.requires_grad_(False)
+    reg = sh.BlockRegistry()
+    reg.build_from_model(model, block_pattern=r"block_\d+", group="test", dtype=dtype)
+    reg.validate(pool_capacity_bytes=10 * 1024 * 1024)
+    q = (torch.arange(64, dtype=torch.int8).reshape(8, 8) - 32).contiguous()
+    bias = torch.arange(8, dtype=torch.float32)
+    path = tmp_path / "tiny.fpk"
+    torch.save({"manifest": {"layers": [{"name": "block_0", "out": 8, "inp": 8, "padded_in": 8, "has_bias": True}]},
+                "layers": {"block_0": {"qweight": q, "scale": torch.ones(8), "zero_point": torch.zeros(8),
+                                       "bias": bias}}}, path)
+    return model, reg, path, q, bias
+
+
+def test_squareq_conversion_bookkeeping(tmp_path: Path) -> None:
+    """Mirrors the reference's conversion test (tests/test_registry.py:202-251)."""
+    model, reg, path, _q, _b = _tiny_fpk(tmp_path)
+    with pytest.raises(RuntimeError):
+        sh.BlockRegistry().convert_to_file_backed(str(path))
+    assert reg.convert_to_file_backed(str(path)) == 2
+    entry = reg.get("block_0")
+    assert entry.file_backed and entry.squareq_backed and entry.source_format == "squareq_bp8"
+    assert len(entry.squareq_param_specs) == 2
+    assert model.block_0.weight.numel() == 0 and model.block_0.bias.numel() == 0
+    assert [row[0] for row in entry.param_layout] == ["weight", "bias"]
+    assert [row[3] for row in entry.param_layout] == [0, 8 * 8 * 4]
+
+
+def test_packed_plan_of_reference_known_answer(tmp_path: Path) -> None:
+    """The reference's known-answer case (tests/test_scheduler.py:294-375): arange weights, unit scale, fp32 runtime."""
+    model, reg, path, q, bias = _tiny_fpk(tmp_path)
+    reg.convert_to_file_backed(str(path))
+    entry = reg.get("block_0")
+    layers = torch.load(path, weights_only=True)["layers"]
+    plan = plan_block_image("block_0", list(entry.param_layout), {s.param_name: s for s in entry.squareq_param_specs},
+                            set(entry.module_param_names), layers, entry.module_ref(), entry.size_bytes)
+    buf = torch.zeros(plan.total_bytes, dtype=torch.uint8)
+    plan.fill_static(buf)
+    out = expand(buf.numpy(), plan.descs, plan.n_descs, entry.size_bytes, plan.out_dtype_code)
+    assert np.array_equal(out[: 64 * 4].view(np.float32).reshape(8, 8), q.float().numpy())
+    assert np.array_equal(out[64 * 4 :].view(np.float32), bias.numpy())
+    assert plan.descs[0].zp_off == -1 and plan.elements == 64
+
+
+def test_packed_plan_matches_reference_stage_block() -> None:
+    """Every branch of the staging control flow, against the slab image the reference produced."""
+    g = np.load(GOLDEN / "stage_block.npz")
+    names = [str(n) for n in g["layout_names"]]
+    shapes = [tuple(int(d) for d in str(s).split(",")) for s in g["layout_shapes"]]
+    layout = [(n, s, torch.bfloat16, int(o), int(k)) for n, s, o, k in
+              zip(names, shapes, g["layout_offsets"], g["layout_numel"])]
+    specs = {str(p): sh.SquareQParamSpec(str(p), str(l), str(k), 0, 0, 0)
+             for p, l, k in zip(g["spec_params"], g["spec_layers"], g["spec_kinds"])}
+    layers: dict[str, dict[str, torch.Tensor]] = {}
+    for key in g.files:
+        if key.startswith("layer__"):
+            _, lname, field = key.split("__")
+            layers.setdefault(lname, {})[field] = torch.from_numpy(g[key].copy())
+
+    class Blk(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.norm = nn.LayerNorm(24)
+            self.proj, self.gate, self.nobias = nn.Linear(24, 40), nn.Linear(24, 8), nn.Linear(24, 16)
+            self.short, self.lost, self.gone = nn.Linear(24, 12), nn.Linear(8, 8), nn.Linear(8, 4)
+
+    blk = Blk()
+    with torch.no_grad():
+        for n, p in blk.named_parameters():
+            p.copy_(torch.from_numpy(g[f"live__{n}"]))
+    blk.lost.weight.data = torch.empty(0)
+    blk.lost.bias.data = torch.empty(0)
+    cache = {k[len("cache__"):]: torch.from_numpy(g[k].copy()) for k in g.files if k.startswith("cache__")}
+    out_bytes = layout[-1][3] + layout[-1][4] * 2
+    plan = plan_block_image("blk", layout, specs, {str(n) for n in g["module_names"]}, layers, blk, out_bytes)
+    buf = torch.zeros(plan.total_bytes, dtype=torch.uint8)
+    plan.fill_static(buf)
+    plan.refresh_dynamic(buf, blk, cache)
+    out = expand(buf.numpy(), plan.descs, plan.n_descs, out_bytes, plan.out_dtype_code)
+    assert np.array_equal(out, g["ref"])
+    assert sorted(cache) == [str(n) for n in g["cache_after"]]
+    # split view: static + rebased dynamic descriptors expand to the same image
+    s_descs, n_s, d_descs, n_d = plan.split_descs()
+    assert n_s + n_d == plan.n_descs and n_d == len(plan.dynamic_rows)
+    out2 = expand(buf.numpy()[: plan.static_bytes], s_descs, n_s, out_bytes, plan.out_dtype_code)
+    dyn = expand(buf.numpy()[plan.static_bytes :], d_descs, n_d, out_bytes, plan.out_dtype_code)
+    merged = np.where(dyn != 0xEE, dyn, out2)
+    touched = (dyn != 0xEE) | (out2 != 0xEE)
+    assert np.array_equal(merged[touched], g["ref"][touched])
+
+
+def test_small_model_images_match_reference_runtime(tmp_path: Path) -> None:
+    """Registry conversion + packed planning on a 3-block model reproduce the reference runtime's block images."""
+    g = np.load(GOLDEN / "runtime_forward.npz")
+    torch.manual_seed(0)
+    model = TinyBlockModel(n_blocks=3, hidden=128, heads=4, mlp=256)
+    for p in model.parameters():
+        p.requires_grad_(False)
+    fpk = tmp_path / "small.fpk"
+    write_squareq_fpk(model, BLOCK_PATTERNS["tiny"], fpk, seed=0)
+    reg = sh.BlockRegistry()
+    reg.build_from_model(model, BLOCK_PATTERNS["tiny"], "t", torch.bfloat16)
+    reg.validate(1 << 30)
+    assert reg.convert_to_file_backed(str(fpk)) == int(g["small__converted"])
+    layers = torch.load(fpk, weights_only=True)["layers"]
+    for entry in reg.blocks_in_order():
+        assert [r[0] for r in entry.param_layout] == [str(n) for n in g["small__layout_names"]]
+        plan = plan_block_image(entry.block_id, list(entry.param_layout),
+                                {s.param_name: s for s in entry.squareq_param_specs},
+                                set(entry.module_param_names), layers, entry.module_ref(), entry.size_bytes)
+        buf = torch.zeros(plan.total_bytes, dtype=torch.uint8)
+        plan.fill_static(buf)
+        plan.refresh_dynamic(buf, entry.module_ref(), {})
+        out = expand(buf.numpy(), plan.descs, plan.n_descs, entry.size_bytes, plan.out_dtype_code)
+        assert np.array_equal(out, g[f"small__image__{entry.block_id}"])
+        assert plan.total_bytes < entry.size_bytes * 0.6     # the image is about half the runtime-dtype slab
+
+
+def test_residency_state_machine_and_pool() -> None:
+    model = TinyBlockModel(n_blocks=2, hidden=32, heads=2, mlp=64)
+    reg = sh.BlockRegistry()
+    reg.build_from_model(model, BLOCK_PATTERNS["tiny"], "t", torch.bfloat16)
+    res = sh.ResidencyMap(reg)
+    with pytest.raises(sh.InvalidStateTransitionError):
+        res.transition("blocks.0", sh.BlockState.GPU_READY)
+    for s in (sh.BlockState.HOST_STAGED, sh.BlockState.PREFETCHING, sh.BlockState.GPU_READY):
+        res.transition("blocks.0", s)
+    res.get_entry("blocks.0").last_used_step = 0
+    assert [b for b, _ in res.eviction_candidates(0, 0)] == ["blocks.0"]
+    res.increment_ref("blocks.0")
+    assert res.eviction_candidates(0, 0) == []
+    res.decrement_ref("blocks.0")
+    with pytest.raises(ValueError):
+        res.decrement_ref("blocks.0")
+
+    pool = sh.PinnedPool(total_mb=4, slab_mb=1)
+    a = pool.acquire(100)
+    many = pool.acquire(3 * 1024 * 1024)
+    assert isinstance(many, list) and len(many) == 3 and pool.stats()["free"] == 0
+    assert pool.try_acquire(10) is None
+    with pytest.raises(sh.StagehandOOMError):
+        pool.acquire(5 * 1024 * 1024)
+    pool.release(many)
+    pool.release(a)
+    assert pool.stats()["in_use"] == 0 and pool.stats()["peak_in_use"] == 4
+    with pytest.raises(sh.StagehandOOMError):
+        reg.validate(pool_capacity_bytes=16)
+
+
+def test_policy_and_budget() -> None:
+    pol = sh.StaticLookaheadPolicy(prefetch_window=3, eviction_cooldown_steps=2)
+    assert pol.blocks_to_prefetch(0, 5, {}) == [1, 2, 3]
+    assert pol.blocks_to_prefetch(3, 5, {}) == [4]
+    assert pol.score_for_eviction("b", 2, 2, 10, 100) == 1000.0
+    assert pol.score_for_eviction("b", 2, 1, 10, 100) == 900.0
+    assert pol.should_evict(0, 3) and not pol.should_evict(1, 3)
+    with pytest.raises(ValueError):
+        sh.BudgetManager(10, 10)
+    b = sh.BudgetManager(100, 50)
+    assert b.vram_used_mb() == 0.0 and b.can_prefetch() and b.below_low_watermark()
+
+
+def test_squareq_load_without_cuda_fails_loudly(tmp_path: Path) -> None:
+    if torch.cuda.is_available():
+        pytest.skip("this check is for hosts without a GPU")
+    torch.manual_seed(0)
+    model = TinyBlockModel(n_blocks=2, hidden=32, heads=2, mlp=64)
+    for p in model.parameters():
+        p.requires_grad_(False)
+    fpk = tmp_path / "m.fpk"
+    write_squareq_fpk(model, BLOCK_PATTERNS["tiny"], fpk)
+    cfg = sh.StagehandConfig(pinned_pool_mb=8, pinned_slab_mb=4, telemetry_enabled=False)
+    rt = sh.StagehandRuntime(model, cfg, block_pattern=BLOCK_PATTERNS["tiny"], inference_mode=True)
+    assert rt.convert_registry_to_file_backed(str(fpk)) == 16
+    rt.begin_step(0)
+    with pytest.raises(sh.TransferError, match="no CPU fallback"):
+        with rt.managed_forward():
+            model(torch.zeros(1, 4, 32, dtype=torch.bfloat16))
+    rt.shutdown()
+
+
+def test_module_backed_block_mode_and_layer_mode_run_on_cpu() -> None:
+    """Module-backed plumbing (no SquareQ source) keeps working without a GPU, as in the reference."""
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Linear(16, 32), nn.ReLU(), nn.Linear(32, 8)).to(torch.bfloat16)
+    ref = model(torch.ones(2, 16, dtype=torch.bfloat16)).clone()
+    wrapped = sh.layer(model, inference_mode=True, telemetry=False, prefetch_k=1)
+    rt = wrapped._stagehand_layer_runtime
+    for _ in range(3):
+        out = wrapped(torch.ones(2, 16, dtype=torch.bfloat16))
+    assert torch.equal(out, ref) and rt.traced and rt.trace_order == ["0", "2"]
+    rt.shutdown()

@@ -113,7 +113,7 @@ class PackedBlockImage:
                 buffer[op.offset : op.offset + op.nbytes].view(t.dtype).copy_(t.reshape(-1))
 
     def refresh_dynamic(self, buffer: torch.Tensor, module: nn.Module | None,
-                        cache: MutableMapping[str, torch.Tensor] | None) -> None:
+                        cache: MutableMapping[str, torch.Tensor] | None, base_offset: int = 0) -> None:
         """Stage the live module-owned parameters (reference ``scheduler.py:310-325``).
 
         A parameter whose element count matches is read from the module (and
@@ -154,7 +154,8 @@ class PackedBlockImage:
                 else:
                     desc.kind, desc.cols = SH_KIND_COPY, row.numel * self.runtime_dtype.itemsize
             nbytes = flat.numel() * flat.element_size()
-            buffer[row.offset : row.offset + nbytes].view(flat.dtype).copy_(flat)
+            at = row.offset - base_offset   # base_offset = static_bytes when *buffer* holds the dynamic section only
+            buffer[at : at + nbytes].view(flat.dtype).copy_(flat)
 
     # ── descriptor views ─────────────────────────────────────────────
 

@@ -551,12 +551,15 @@ class StagehandScheduler:
 
     def _stage_dynamic_only(self, entry: "BlockEntry", plan: "PackedBlockImage") -> tuple["HostImage", Any]:
         """Host image that only carries the dynamic section (the static one is resident in HBM)."""
-        image = self._image_store.get(entry.block_id) or self._image_store.create(entry.block_id, plan.total_bytes)
+        key = entry.block_id + "#dynamic"
+        nbytes = plan.total_bytes - plan.static_bytes
+        image = self._image_store.get(key) or self._image_store.create(key, nbytes)
         if image is None:
             raise StagehandOOMError(f"no pinned memory left for the dynamic section of block {entry.block_id!r}")
         if image.last_copy is not None and not image.last_copy.done():
             image.last_copy.wait(60_000)
-        plan.refresh_dynamic(image.buffer, entry.module_ref(), self._module_param_caches.setdefault(entry.block_id, {}))
+        plan.refresh_dynamic(image.buffer, entry.module_ref(), self._module_param_caches.setdefault(entry.block_id, {}),
+                             base_offset=plan.static_bytes)
         return image, None
 
     def set_device_sources(self, sources: dict[str, tuple[int, bool]], fused: bool = True) -> None:

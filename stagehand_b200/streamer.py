@@ -197,7 +197,8 @@ class Int8BlockStreamer:
         (plain peer loads when it is another GPU's memory) -- gather and dequant in
         one kernel, no staging copy.  ``fused=False``: a copy-engine pull into the
         local staging slab first, then the kernel.  The dynamic section (live
-        module-owned parameters), if any, always comes from local host memory.
+        module-owned parameters), if any, always comes from local host memory
+        (*dynamic_host* holds that section only).
         """
         static_descs, n_static, dyn_descs, n_dyn = image.split_descs()
         self._order_output(out_slab)
@@ -240,7 +241,7 @@ class Int8BlockStreamer:
             dyn_copied = acquire_event()
             dyn_ready = acquire_event()
             _native.check(self._lib.sh_stream_block_async(
-                dyn_descs, n_dyn, dynamic_host.buffer.data_ptr() + image.static_bytes, dyn_bytes,
+                dyn_descs, n_dyn, dynamic_host.buffer.data_ptr(), dyn_bytes,
                 dyn_stage.tensor.data_ptr(), out_slab.tensor.data_ptr(), image.out_bytes, image.out_dtype_code,
                 stream_handle(self.copy_stream), dq, dyn_copied.handle, dyn_ready.handle, self.status.data_ptr()),
                 f"dynamic section of {image.block_id}")

@@ -1,0 +1,146 @@
+"""GPU end-to-end parity of the streaming runtime against the reference runtime's captured results.
+
+Golden data: ``tests/golden/runtime_forward.npz`` (the reference's CPU block-mode run on the same seeded
+model, slab and input).  Bars: block images bit-exact; forward output within 1e-2 relative L2 (bf16).
+"""
+from __future__ import annotations
+
+import hashlib
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN
+import stagehand_b200 as sh
+from stagehand_b200.workloads import BLOCK_PATTERNS, TinyBlockModel, write_squareq_fpk
+
+pytestmark = pytest.mark.gpu
+
+G = np.load(GOLDEN / "runtime_forward.npz")
+CFGS = {
+    "cfg1": (dict(n_blocks=4, hidden=1024, heads=16, mlp=4096), 256),
+    "small": (dict(n_blocks=3, hidden=128, heads=4, mlp=256), 32),
+}
+
+
+def _build(tag: str, tmp_path: Path, **cfg_kw):
+    kw, tokens = CFGS[tag]
+    torch.manual_seed(0)
+    model = TinyBlockModel(**kw)
+    for p in model.parameters():
+        p.requires_grad_(False)
+    fpk = tmp_path / f"{tag}.fpk"
+    write_squareq_fpk(model, BLOCK_PATTERNS["tiny"], fpk, seed=0)
+    base = dict(pinned_pool_mb=256, pinned_slab_mb=64, telemetry_enabled=True, telemetry_file=str(tmp_path / "t.jsonl"),
+                nan_inf_check=False, prefetch_window_blocks=3)
+    base.update(cfg_kw)
+    rt = sh.StagehandRuntime(model, sh.StagehandConfig(**base), block_pattern=BLOCK_PATTERNS["tiny"], group="t",
+                             dtype=torch.bfloat16, inference_mode=True)
+    assert rt.convert_registry_to_file_backed(str(fpk)) == int(G[f"{tag}__converted"])
+    x = torch.randn(1, tokens, kw["hidden"], generator=torch.Generator().manual_seed(0)).to(torch.bfloat16).cuda()
+    return model, rt, x
+
+
+def _rel_l2(y: torch.Tensor, tag: str) -> float:
+    rows = torch.from_numpy(G[f"{tag}__y_rows"])
+    ref = torch.from_numpy(G[f"{tag}__y_sample"].view(np.int16).copy()).view(torch.bfloat16).float()
+    got = y[0].float().cpu()[rows]
+    return float((got - ref).norm() / ref.norm())
+
+
+@pytest.mark.parametrize("tag", ["small", "cfg1"])
+def test_streamed_forward_matches_reference(tag: str, tmp_path: Path) -> None:
+    model, rt, x = _build(tag, tmp_path)
+    rt.begin_step(0)
+    with torch.inference_mode(), rt.managed_forward():
+        y = model(x)
+    torch.cuda.synchronize()
+    # every block image in VRAM is bit-identical to the slab the reference's host dequant produced
+    digests = []
+    for entry in rt._registry.blocks_in_order():
+        res = rt._residency.get_entry(entry.block_id)
+        assert res.state is sh.BlockState.GPU_READY
+        img = res.gpu_tensor.view(torch.uint8).cpu().numpy()
+        digests.append(hashlib.sha256(img.tobytes()).hexdigest())
+        assert entry.size_bytes == int(G[f"{tag}__block_bytes"][entry.exec_order])
+    assert digests == [str(d) for d in G[f"{tag}__block_sha256"]]
+    assert rt._scheduler._streamer.read_status() == 0
+    rt.end_step()
+    assert _rel_l2(y, tag) <= 1e-2
+    m = rt.telemetry.last()
+    assert m.dequant_launches == len(rt._registry) and m.h2d_bytes == sum(int(b) for b in G[f"{tag}__block_bytes"])
+    assert 0 < m.link_bytes < 0.55 * m.h2d_bytes        # packed INT8 crossed the link, not bf16
+    # module parameters are views into the pooled slab
+    w = model.blocks[0].qkv.weight
+    assert w.is_cuda and w.dtype == torch.bfloat16 and tuple(w.shape) == (3 * CFGS[tag][0]["hidden"], CFGS[tag][0]["hidden"])
+    rt.shutdown()
+
+
+@pytest.mark.parametrize("cache_mb", [-1, 0])
+def test_eviction_and_reload_under_a_tight_budget(cache_mb: int, tmp_path: Path) -> None:
+    """Watermarks below one block: every block is evicted after use and reloaded on each step."""
+    model, rt, x = _build("cfg1", tmp_path, vram_high_watermark_mb=2, vram_low_watermark_mb=1,
+                          packed_image_cache_mb=cache_mb, prefetch_window_blocks=2)
+    outs = []
+    for step in range(4):
+        rt.begin_step(step)
+        with torch.inference_mode(), rt.managed_forward():
+            outs.append(model(x))
+        rt.end_step()
+    torch.cuda.synchronize()
+    assert rt._scheduler._streamer.read_status() == 0
+    for y in outs:
+        assert _rel_l2(y, "cfg1") <= 1e-2
+        assert torch.equal(y, outs[0])                   # reloads are deterministic
+    last = rt.telemetry.last()
+    assert last.evictions >= 3 and last.dequant_launches == 4
+    pool = rt._scheduler._device_pool
+    assert pool.reuses > 0 and pool.allocations <= 6     # slabs are recycled, not reallocated per load
+    if cache_mb == 0:
+        assert len(rt._scheduler._image_store) == 0 and rt._pool.stats()["peak_in_use"] >= 1
+    else:
+        assert len(rt._scheduler._image_store) == 4 and last.image_cache_hits == 4
+    # evicted blocks leave empty frozen parameters behind, as in the reference
+    evicted = [e for e in rt._registry.blocks_in_order()
+               if rt._residency.get_state(e.block_id) is sh.BlockState.UNLOADED]
+    assert evicted and all(e.module_ref().qkv.weight.numel() == 0 for e in evicted)
+    assert all(e.module_ref().norm1.weight.numel() == 1024 for e in evicted)   # module-owned params survive
+    rt.shutdown()
+    assert rt._pool.stats()["in_use"] == 0 if cache_mb else True
+
+
+def test_resident_blocks_are_hits_on_later_steps(tmp_path: Path) -> None:
+    model, rt, x = _build("small", tmp_path)
+    for step in range(3):
+        rt.begin_step(step)
+        with torch.inference_mode(), rt.managed_forward():
+            model(x)
+        rt.end_step()
+    last = rt.telemetry.last()
+    assert last.prefetch_hits == 3 and last.prefetch_misses == 0 and last.dequant_launches == 0
+    rt.shutdown()
+
+
+def test_device_resident_images_fused_and_staged(tmp_path: Path) -> None:
+    """INT8 images parked in HBM (the single-GPU form of the sharded layout): same bits, no host-link bytes."""
+    from stagehand_b200.sharded import park_images_in_hbm
+
+    for fused in (True, False):
+        model, rt, x = _build("cfg1", tmp_path)
+        store = park_images_in_hbm(rt, fused=fused)
+        rt.begin_step(0)
+        with torch.inference_mode(), rt.managed_forward():
+            y = model(x)
+        torch.cuda.synchronize()
+        assert _rel_l2(y, "cfg1") <= 1e-2
+        entry = rt._registry.blocks_in_order()[-1]
+        res = rt._residency.get_entry(entry.block_id)
+        img = res.gpu_tensor.view(torch.uint8).cpu().numpy()
+        assert hashlib.sha256(img.tobytes()).hexdigest() == str(G["cfg1__block_sha256"][-1])
+        m = rt._telemetry._current
+        assert m.link_bytes < 4 * 20_000        # only the module-owned norm parameters cross the host link
+        rt.end_step()
+        rt.shutdown()
+        store.close()

@@ -334,3 +334,21 @@ def write_squareq_fpk(model: nn.Module, block_pattern: str, path: str | Path, se
     }
     torch.save(payload, str(path))
     return {"layers": len(manifest_layers), "elements": elements}
+
+
+def materialize_small_params(model: nn.Module) -> None:
+    """Give real CPU storage to the parameters of a meta-device model that no slab will ever fill.
+
+    Large synthetic models are built on the ``meta`` device so that their projections
+    (filled from the SquareQ slab at load time) never occupy host memory; the small
+    module-owned parameters -- normalisation weights and biases -- need actual values:
+    weights become ones, biases zeros.
+    """
+    for module in model.modules():
+        if isinstance(module, nn.Linear):
+            continue
+        for name, param in list(module.named_parameters(recurse=False)):
+            if param.device.type != "meta":
+                continue
+            fill = torch.zeros if name.endswith("bias") else torch.ones
+            setattr(module, name, nn.Parameter(fill(param.shape, dtype=param.dtype), requires_grad=False))

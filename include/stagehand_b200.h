@@ -243,6 +243,33 @@ int32_t sh_profile_enable(int32_t on);
 int32_t sh_profile_collect(double* kernel_ms_out, int64_t* launches_out, int64_t* elements_out,
                            int64_t* bytes_out, int32_t timeout_ms);
 
+/*
+ * Host image -> runtime-dtype weights in VRAM for callers that cannot allocate device memory on this
+ * path (a process whose GPU memory was handed to another allocator at start-up, a plug-in that must
+ * not grow its footprint, a loop where an allocation would stall the device).  It is
+ * sh_stream_block_async on ONE stream with the staging slab replaced by a fixed array inside the
+ * library's device image: SH_NOALLOC_MAX_BYTES per GPU that loads the library, held until exit.
+ * It calls no cudaMalloc / cudaFree and no allocating library routine; the caller passes the host
+ * image and the output slab as usual.
+ *
+ *   - packed_bytes above SH_NOALLOC_MAX_BYTES (or more than 128 descriptors) fails with
+ *     SH_ERR_INVALID_ARG and a message; nothing is enqueued.
+ *   - The first call on a device resolves the array's device address (cudaGetSymbolAddress) with
+ *     that device current; make that first call before any stream capture begins.
+ *   - Every call shares the one array, which keeps the previous call's bytes.  Nothing in it has to
+ *     start at zero -- each call overwrites every byte its kernel reads -- but two calls whose GPU
+ *     work overlaps (different streams, no ordering between them) race on it: serialise them.
+ *   - Failure text: sh_noalloc_last_error (this entry point keeps its own per-thread message).
+ *
+ * This entry point has no counterpart in the reference.
+ */
+#define SH_NOALLOC_MAX_BYTES (32 * 1024 * 1024)
+int32_t sh_dequant_from_host_noalloc(const ShParamDesc* descs, int32_t n_descs,
+                                     const void* packed_host, size_t packed_bytes,
+                                     void* out_dev, size_t out_bytes, int32_t out_dtype,
+                                     uint64_t stream, int32_t* status_dev);
+int32_t sh_noalloc_last_error(char* buf, int32_t buf_len);
+
 #ifdef __cplusplus
 }
 #endif

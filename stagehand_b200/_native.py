@@ -24,6 +24,7 @@ SH_OK, SH_ERR_INVALID_ARG, SH_ERR_OOM, SH_ERR_CUDA, SH_ERR_TIMEOUT, SH_ERR_BUSY,
 SH_KIND_DEQUANT_I8, SH_KIND_CAST_F32, SH_KIND_COPY, SH_KIND_ZERO = 0, 1, 2, 3
 SH_DT_BF16, SH_DT_F16, SH_DT_F32 = 0, 1, 2
 SH_DESC_PEER_SOURCE = 1
+SH_NOALLOC_MAX_BYTES = 32 * 1024 * 1024
 
 
 class ShParamDesc(ctypes.Structure):
@@ -87,6 +88,9 @@ _SIGNATURES: dict[str, list] = {
     "sh_dequant_block_async": [_P_DESC, c_int32, c_void_p, c_size_t, c_void_p, c_size_t, c_int32, c_uint64, c_void_p],
     "sh_stream_block_async": [_P_DESC, c_int32, c_void_p, c_size_t, c_void_p, c_void_p, c_size_t, c_int32,
                               c_uint64, c_uint64, c_uint64, c_uint64, c_void_p],
+    "sh_dequant_from_host_noalloc": [_P_DESC, c_int32, c_void_p, c_size_t, c_void_p, c_size_t, c_int32, c_uint64,
+                                     c_void_p],
+    "sh_noalloc_last_error": [c_char_p, c_int32],
     "sh_profile_enable": [c_int32],
     "sh_profile_collect": [POINTER(c_double), POINTER(c_int64), POINTER(c_int64), POINTER(c_int64), c_int32],
 }

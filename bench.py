@@ -48,7 +48,8 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="flux", choices=["flux", "flux_small", "flux+mistral"])
+    ap.add_argument("--workload", default="flux", choices=["flux", "flux_small", "kernel_sweep"])
+    ap.add_argument("--shapes", default="", help="kernel_sweep: comma-separated NxK list (default: the full sweep)")
     ap.add_argument("--prefetch-k", type=int, default=3)
     ap.add_argument("--vram-budget-gb", type=float, default=8.0)
     ap.add_argument("--no-fused", action="store_true", help="multi-GPU: copy-engine pull + kernel instead of the fused kernel")
@@ -310,6 +311,83 @@ def run_reference_arm(args) -> None:
     print(json.dumps(line), flush=True)
 
 
+# ── kernel sweep (device-resident dequant and H2D + dequant per matrix shape) ──
+
+SWEEP_SHAPES = [(1024, 1024), (2048, 2048), (4096, 4096), (8192, 8192), (3072, 3072), (9216, 3072), (12288, 3072),
+                (3072, 12288), (21504, 3072), (3072, 15360), (18432, 3072), (6144, 6144), (12288, 12288),
+                (12288, 49152)]
+
+
+def run_kernel_sweep(args) -> None:
+    """One weight matrix per launch through the C ABI: GB/s at 3 B/weight, L2 flushed between iterations."""
+    import ctypes
+
+    import torch
+
+    from stagehand_b200 import _native as native
+    from stagehand_b200._native import ShParamDesc
+
+    lib = native.lib()
+    native.check(lib.sh_init(torch.cuda.current_device()), "sh_init")
+    peaks = measured_peaks()
+    shapes = SWEEP_SHAPES
+    if args.shapes:
+        shapes = [tuple(int(v) for v in item.lower().split("x")) for item in args.shapes.split(",")]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    link_peak = probe_host_link(256 << 20)
+    rows_out = []
+    for n, k in shapes:
+        gen = torch.Generator(device="cuda").manual_seed(n * 131 + k)
+        scale_off = -(-(n * k) // 256) * 256
+        nbytes = scale_off + -(-n // 4) * 16 + 256
+        img = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+        img[: n * k] = torch.randint(-127, 128, (n * k,), dtype=torch.int8, device="cuda", generator=gen).view(torch.uint8)
+        scale = torch.exp(torch.randn(n, device="cuda", generator=gen) * 0.5 - 4.605).float()
+        img[scale_off : scale_off + n * 4] = scale.view(torch.uint8)
+        out = torch.empty(n * k, dtype=torch.bfloat16, device="cuda")
+        descs = native.make_descs([ShParamDesc(kind=0, flags=0, src_off=0, scale_off=scale_off, zp_off=-1, dst_off=0,
+                                               rows=n, cols=k, ld=k)])
+
+        def resident():
+            native.check(lib.sh_dequant_block_async(descs, 1, img.data_ptr(), nbytes, out.data_ptr(), n * k * 2, 0,
+                                                    stream, None), "sh_dequant_block_async")
+
+        host = img.cpu().pin_memory()
+        staging = torch.empty_like(img)
+
+        def from_host():
+            native.check(lib.sh_stream_block_async(descs, 1, host.data_ptr(), nbytes, staging.data_ptr(), out.data_ptr(),
+                                                   n * k * 2, 0, stream, stream, 0, 0, None), "sh_stream_block_async")
+
+        def timeit(fn):
+            for _ in range(max(args.warmup, 1)):
+                fn()
+            ts = []
+            for _ in range(max(args.steps, 1)):
+                flush.zero_()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                fn()
+                e1.record()
+                torch.cuda.synchronize()
+                ts.append(e0.elapsed_time(e1))
+            return statistics.median(ts)
+
+        ms_res, ms_host = timeit(resident), timeit(from_host)
+        ref = (img[: n * k].view(torch.int8).view(n, k).float() * scale[:, None]).to(torch.bfloat16)
+        exact = bool(torch.equal(ref.view(torch.int16), out.view(n, k).view(torch.int16)))
+        gbs = 3.0 * n * k / ms_res / 1e6
+        rows_out.append({"shape": [n, k], "resident_ms": ms_res, "resident_gbs": gbs, "hbm_frac": gbs / peaks["hbm_gbs"],
+                         "h2d_dequant_ms": ms_host, "link_gbs": nbytes / ms_host / 1e6,
+                         "link_frac": nbytes / ms_host / 1e6 / link_peak, "bit_exact_vs_torch": exact})
+        del img, out, host, staging, ref
+    print(json.dumps({"metric": "dequant_kernel_sweep", "unit": "GB/s", "hbm_peak_gbs": peaks["hbm_gbs"],
+                      "hbm_peak_source": peaks["source"], "host_link_peak_gbs": link_peak, "steps": args.steps,
+                      "warmup": args.warmup, "l2": "256 MiB written between timed iterations", "shapes": rows_out}),
+          flush=True)
+
+
 # ── main ─────────────────────────────────────────────────────────────────
 
 
@@ -331,6 +409,11 @@ def main() -> None:
     import torch
 
     from stagehand_b200 import _native as native
+
+    if args.workload == "kernel_sweep":
+        if int(os.environ.get("RANK", "0")) == 0:
+            run_kernel_sweep(args)
+        return
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))

@@ -9,6 +9,7 @@ of freeing it) would never bring usage below the low watermark.
 """
 from __future__ import annotations
 
+import time
 from typing import Callable
 
 import torch
@@ -26,15 +27,27 @@ class BudgetManager:
         self._high_watermark_mb = high_watermark_mb
         self._low_watermark_mb = low_watermark_mb
         self._credit_bytes: Callable[[], int] | None = None
+        # torch.cuda.memory_allocated() assembles the allocator's whole statistics table on every call
+        # (tens of microseconds); the scheduler asks several times per block, so the reading is reused
+        # for a short time.  invalidate() drops it (the device pool calls it when it really allocates).
+        self._reading_ttl_s = 0.0005
+        self._reading: tuple[float, int] | None = None
 
     def set_reusable_bytes_source(self, fn: Callable[[], int] | None) -> None:
         """Register a callable returning allocator-visible bytes that are free for reuse."""
         self._credit_bytes = fn
 
+    def invalidate(self) -> None:
+        """Forget the cached allocator reading (call after a large allocation or free)."""
+        self._reading = None
+
     def vram_used_mb(self) -> float:
         if not torch.cuda.is_available():
             return 0.0
-        used = torch.cuda.memory_allocated()
+        now = time.monotonic()
+        if self._reading is None or now - self._reading[0] > self._reading_ttl_s:
+            self._reading = (now, torch.cuda.memory_allocated())
+        used = self._reading[1]
         if self._credit_bytes is not None:
             used = max(0, used - int(self._credit_bytes()))
         return used / _MB

@@ -13,7 +13,8 @@
 // fast path issues one 16-byte coalesced load per lane (16 weights), stages the
 // tile's scale rows in shared memory with a bulk asynchronous copy (TMA engine,
 // completion on an mbarrier with a bounded wait) while those loads are in
-// flight, and writes two 16-byte stores per load.
+// flight (only for tiles that span many rows; long rows read their few scales with cached loads),
+// and writes one 32-byte store per load (two 16-byte stores when the destination is not 32-byte aligned).
 #include "sq_block_kernel.cuh"
 
 #include <cstdio>
@@ -95,6 +96,13 @@ __device__ __forceinline__ void store16(void* p, const uint4& v) {
                  : "memory");
 }
 
+// One 32-byte store (sm_100: 256-bit global stores); `p` must be 32-byte aligned.
+__device__ __forceinline__ void store32(void* p, const uint4& a, const uint4& b) {
+    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(a.x), "r"(a.y), "r"(a.z),
+                 "r"(a.w), "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w)
+                 : "memory");
+}
+
 // ── conversion ───────────────────────────────────────────────────────────
 
 // Byte k of `w` (a signed int8) as an exact fp32: bias the byte to unsigned,
@@ -143,7 +151,7 @@ struct Pack<float> {
 
 // 16 int8 (one int4) -> 16 outputs at dst (16-byte aligned).
 template <typename OutT, bool HasZp>
-__device__ __forceinline__ void convert_store16(const int4& q, float scale, float zp, uint8_t* dst) {
+__device__ __forceinline__ void convert_store16(const int4& q, float scale, float zp, uint8_t* dst, bool wide) {
     const uint32_t w[4] = {static_cast<uint32_t>(q.x) ^ 0x80808080u, static_cast<uint32_t>(q.y) ^ 0x80808080u,
                            static_cast<uint32_t>(q.z) ^ 0x80808080u, static_cast<uint32_t>(q.w) ^ 0x80808080u};
     float f[16];
@@ -164,8 +172,12 @@ __device__ __forceinline__ void convert_store16(const int4& q, float scale, floa
         hi.y = Pack<OutT>::two(f[10], f[11]);
         hi.z = Pack<OutT>::two(f[12], f[13]);
         hi.w = Pack<OutT>::two(f[14], f[15]);
-        store16(dst, lo);
-        store16(dst + 16, hi);
+        if (wide) {
+            store32(dst, lo, hi);
+        } else {
+            store16(dst, lo);
+            store16(dst + 16, hi);
+        }
     } else {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -181,25 +193,74 @@ __device__ __forceinline__ void convert_store16(const int4& q, float scale, floa
 
 // ── tile bodies ──────────────────────────────────────────────────────────
 
-template <typename OutT, bool HasZp>
+// row offset (within the tile's first row) of in-tile vector index t: t / segs_per_row without a division
+__device__ __forceinline__ uint32_t tile_row_of(uint32_t t, uint32_t spr, uint64_t magic) {
+    if (magic != 0) return static_cast<uint32_t>((static_cast<uint64_t>(t) * magic) >> 32);
+    return t >= spr ? 1u : 0u;
+}
+
+template <typename OutT, bool HasZp, bool Dense>
 __device__ __forceinline__ void dequant_vec_tile(const DescDev& D, int64_t local_tile, float* s_scale, float* s_zp,
                                                  uint64_t* s_bar, int32_t* status) {
     const uint32_t spr = static_cast<uint32_t>(D.segs_per_row);
+    const uint64_t magic = D.row_magic;
     const int64_t total_segs = D.rows * static_cast<int64_t>(spr);
     const int64_t seg0 = local_tile * kTileSegs;
     const int64_t remaining = total_segs - seg0;
     const uint32_t n_segs = remaining < kTileSegs ? static_cast<uint32_t>(remaining) : kTileSegs;
-    const int64_t row_first = seg0 / spr;
-    const uint32_t cseg_first = static_cast<uint32_t>(seg0 - row_first * spr);
-    const uint32_t rows_in_tile = (cseg_first + n_segs - 1) / spr + 1;
+    const bool peer = (D.flags & SH_DESC_PEER_SOURCE) != 0;
+    const bool wide = (D.flags & kFlagStore32) != 0;
 
+    int4 q[kSegsPerThread];
+    uint32_t row_off[kSegsPerThread];
+    uint32_t cseg[kSegsPerThread];
+    int64_t row_first;
+    uint32_t cseg_first;
+
+    if (Dense) {
+        // Contiguous rows: the address of a vector does not depend on its row, so every load is
+        // issued before any index arithmetic; rows are only needed to pick the scale.
+        const uint8_t* base = D.src + seg0 * kSegBytes;
+#pragma unroll
+        for (int i = 0; i < kSegsPerThread; ++i) {
+            const uint32_t o = threadIdx.x + i * kThreads;
+            if (o < n_segs) {
+                const uint8_t* p = base + static_cast<uint32_t>(o * kSegBytes);
+                q[i] = peer ? load_plain16(p) : load_stream16(p);
+            } else {
+                q[i] = make_int4(0, 0, 0, 0);
+            }
+        }
+        row_first = seg0 / spr;
+        cseg_first = static_cast<uint32_t>(seg0 - row_first * spr);
+#pragma unroll
+        for (int i = 0; i < kSegsPerThread; ++i) row_off[i] = tile_row_of(cseg_first + threadIdx.x + i * kThreads, spr, magic);
+    } else {
+        row_first = seg0 / spr;
+        cseg_first = static_cast<uint32_t>(seg0 - row_first * spr);
+#pragma unroll
+        for (int i = 0; i < kSegsPerThread; ++i) {
+            const uint32_t o = threadIdx.x + i * kThreads;
+            const uint32_t t = cseg_first + o;
+            row_off[i] = tile_row_of(t, spr, magic);
+            cseg[i] = t - row_off[i] * spr;
+            if (o < n_segs) {
+                const uint8_t* p = D.src + (row_first + row_off[i]) * D.ld + static_cast<int64_t>(cseg[i]) * kSegBytes;
+                q[i] = peer ? load_plain16(p) : load_stream16(p);
+            } else {
+                q[i] = make_int4(0, 0, 0, 0);
+            }
+        }
+    }
+
+    const uint32_t rows_in_tile = (cseg_first + n_segs - 1) / spr + 1;
     // rows staged in shared memory: [r_lo, r_lo + n_stage), r_lo aligned down to 4 rows (16 bytes)
     const int64_t r_lo = row_first & ~int64_t(3);
     const uint32_t lead = static_cast<uint32_t>(row_first - r_lo);
     const uint32_t n_stage = (lead + rows_in_tile + 3u) & ~3u;
-    const bool peer = (D.flags & SH_DESC_PEER_SOURCE) != 0;
-    bool staged = (D.flags & kFlagBulkScales) != 0 && n_stage <= kSmemRows;
-
+    // Staging pays when a tile spans many scale rows (short rows); with long rows a tile needs a
+    // handful of scales and plain cached loads are cheaper than a barrier round trip.
+    bool staged = (D.flags & kFlagBulkScales) != 0 && rows_in_tile >= kStageMinRows && n_stage <= kSmemRows;
     if (staged) {
         if (threadIdx.x == 0) {
             mbar_init(s_bar, 1);
@@ -212,24 +273,6 @@ __device__ __forceinline__ void dequant_vec_tile(const DescDev& D, int64_t local
         __syncthreads();   // barrier initialised before anyone polls it
     }
 
-    // issue every weight load of this thread before touching the scales
-    int4 q[kSegsPerThread];
-    uint32_t row_off[kSegsPerThread];
-    uint32_t cseg[kSegsPerThread];
-#pragma unroll
-    for (int i = 0; i < kSegsPerThread; ++i) {
-        const uint32_t o = threadIdx.x + i * kThreads;
-        const uint32_t t = cseg_first + o;
-        row_off[i] = t / spr;
-        cseg[i] = t - row_off[i] * spr;
-        if (o < n_segs) {
-            const uint8_t* p = D.src + (row_first + row_off[i]) * D.ld + static_cast<int64_t>(cseg[i]) * kSegBytes;
-            q[i] = peer ? load_plain16(p) : load_stream16(p);
-        } else {
-            q[i] = make_int4(0, 0, 0, 0);
-        }
-    }
-
     bool timed_out = false;
     if (staged && !mbar_wait_bounded(s_bar, 0)) {
         staged = false;   // fall back to plain loads for this thread; the result stays correct
@@ -237,21 +280,22 @@ __device__ __forceinline__ void dequant_vec_tile(const DescDev& D, int64_t local
         if (status != nullptr) atomicOr(status, kStatusBulkTimeout);
     }
 
+    // the destination is dense in every case: output vector i of the matrix is at dst + i * 16 * sizeof(OutT)
+    uint8_t* out_base = D.dst + seg0 * (kSegBytes * sizeof(OutT));
 #pragma unroll
     for (int i = 0; i < kSegsPerThread; ++i) {
         const uint32_t o = threadIdx.x + i * kThreads;
         if (o >= n_segs) continue;
-        const int64_t row = row_first + row_off[i];
         float s, z = 0.0f;
         if (staged) {
             s = s_scale[lead + row_off[i]];
             if (HasZp) z = s_zp[lead + row_off[i]];
         } else {
-            s = D.scale[row];
-            if (HasZp) z = D.zp[row];
+            const int64_t row = row_first + row_off[i];
+            s = peer ? D.scale[row] : __ldg(D.scale + row);
+            if (HasZp) z = peer ? D.zp[row] : __ldg(D.zp + row);
         }
-        uint8_t* dst = D.dst + (row * D.cols + static_cast<int64_t>(cseg[i]) * kSegBytes) * sizeof(OutT);
-        convert_store16<OutT, HasZp>(q[i], s, z, dst);
+        convert_store16<OutT, HasZp>(q[i], s, z, out_base + static_cast<size_t>(o) * (kSegBytes * sizeof(OutT)), wide);
     }
     // A copy that was still in flight when the wait gave up targets this CTA's shared
     // memory: give it one more bounded chance to land before the CTA retires.
@@ -329,7 +373,7 @@ __device__ __forceinline__ void copy_zero_tile(const DescDev& D, int64_t local_t
 // ── the kernel ───────────────────────────────────────────────────────────
 
 template <typename OutT>
-__global__ void __launch_bounds__(kThreads) sq_block_kernel(const __grid_constant__ BlockPlan plan, int32_t* status) {
+__global__ void __launch_bounds__(kThreads, SQ_MIN_CTAS_PER_SM) sq_block_kernel(const __grid_constant__ BlockPlan plan, int32_t* status) {
     __shared__ alignas(16) float s_scale[kSmemRows];
     __shared__ alignas(16) float s_zp[kSmemRows];
     __shared__ alignas(8) uint64_t s_bar;
@@ -342,8 +386,13 @@ __global__ void __launch_bounds__(kThreads) sq_block_kernel(const __grid_constan
 
     switch (D.path) {
         case kPathDequantVec:
-            if (D.zp != nullptr) dequant_vec_tile<OutT, true>(D, local_tile, s_scale, s_zp, &s_bar, status);
-            else                 dequant_vec_tile<OutT, false>(D, local_tile, s_scale, s_zp, &s_bar, status);
+            if (D.flags & kFlagDense) {
+                if (D.zp != nullptr) dequant_vec_tile<OutT, true, true>(D, local_tile, s_scale, s_zp, &s_bar, status);
+                else                 dequant_vec_tile<OutT, false, true>(D, local_tile, s_scale, s_zp, &s_bar, status);
+            } else {
+                if (D.zp != nullptr) dequant_vec_tile<OutT, true, false>(D, local_tile, s_scale, s_zp, &s_bar, status);
+                else                 dequant_vec_tile<OutT, false, false>(D, local_tile, s_scale, s_zp, &s_bar, status);
+            }
             break;
         case kPathDequantScalar: dequant_scalar_tile<OutT>(D, local_tile); break;
         case kPathCastVec:       cast_tile<OutT>(D, local_tile, true); break;
@@ -444,6 +493,10 @@ int build_plans(const ShParamDesc* descs, int n, const void* packed, size_t pack
                                          u.scale_off + rows4 * 4 <= pbytes &&
                                          (D.zp == nullptr || (aligned(D.zp, 16) && u.zp_off + rows4 * 4 <= pbytes));
                     if (bulk_ok) D.flags |= kFlagBulkScales;
+                    if (osz == 2 && aligned(obase + u.dst_off, 32)) D.flags |= kFlagStore32;
+                    if (u.ld == u.cols) D.flags |= kFlagDense;
+                    const uint64_t spr64 = static_cast<uint64_t>(D.segs_per_row);
+                    D.row_magic = ((spr64 + kTileSegs) * spr64 < (uint64_t(1) << 32)) ? ((uint64_t(1) << 32) / spr64 + 1) : 0;
                 } else {
                     D.path = kPathDequantScalar;
                     n_tiles = ceil_div(u.rows * u.cols, kTileItems);

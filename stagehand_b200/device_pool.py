@@ -33,8 +33,11 @@ class DeviceSlab:
 class DeviceSlabPool:
     """Exact-size free lists of output slabs (one list per distinct block size)."""
 
-    def __init__(self, device: torch.device | str = "cuda", max_parked_bytes: int | None = None) -> None:
+    def __init__(self, device: torch.device | str = "cuda", max_parked_bytes: int | None = None,
+                 on_allocation=None, on_trim=None) -> None:
         self._device = torch.device(device)
+        self._on_allocation = on_allocation       # called after the allocator-visible total changed
+        self._on_trim = on_trim                   # called before parked slabs are dropped (holders of views let go)
         self._free: dict[int, list[DeviceSlab]] = {}
         self._parked_bytes = 0
         self._max_parked = max_parked_bytes
@@ -57,6 +60,8 @@ class DeviceSlabPool:
             tensor = torch.empty(nbytes, dtype=torch.uint8, device=self._device)
         self.allocations += 1
         self._next_id += 1
+        if self._on_allocation is not None:
+            self._on_allocation()
         slab = DeviceSlab(tensor=tensor, nbytes=nbytes, slab_id=self._next_id)
         if self._device.type == "cuda":
             # The caching allocator may hand back memory that kernels already queued on the
@@ -84,8 +89,12 @@ class DeviceSlabPool:
 
     def trim(self) -> None:
         """Give every parked slab back to the allocator."""
+        if self._on_trim is not None:
+            self._on_trim()
         self._free.clear()
         self._parked_bytes = 0
+        if self._on_allocation is not None:
+            self._on_allocation()
 
 
 class StagingRing:

@@ -88,6 +88,7 @@ class PackedBlockImage:
     n_descs: int = 0
     static_ops: list[_StaticOp] = field(default_factory=list)
     dynamic_rows: list[_DynamicRow] = field(default_factory=list)
+    _static_split: Any = None
 
     @property
     def out_dtype_code(self) -> int:
@@ -166,14 +167,16 @@ class PackedBlockImage:
         (an INT8 image resident in this or another GPU's HBM).
         """
         dyn_index = {row.desc_index for row in self.dynamic_rows}
-        static = [self.descs[i] for i in range(self.n_descs) if i not in dyn_index]
+        if self._static_split is None:     # static descriptors never change: build their array once
+            static = [self.descs[i] for i in range(self.n_descs) if i not in dyn_index]
+            self._static_split = (_native.make_descs(static), len(static))
         dynamic = []
         for i in sorted(dyn_index):
             d = ShParamDesc()
             ctypes.memmove(ctypes.byref(d), ctypes.byref(self.descs[i]), ctypes.sizeof(ShParamDesc))
             d.src_off -= self.static_bytes
             dynamic.append(d)
-        return _native.make_descs(static), len(static), _native.make_descs(dynamic), len(dynamic)
+        return self._static_split[0], self._static_split[1], _native.make_descs(dynamic), len(dynamic)
 
 
 def _flat_f32(t: torch.Tensor) -> torch.Tensor:

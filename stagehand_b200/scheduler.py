@@ -24,6 +24,7 @@ import mmap
 import os
 import time
 from pathlib import Path
+from collections.abc import Mapping
 from typing import TYPE_CHECKING, Any, Protocol
 
 import torch
@@ -136,6 +137,22 @@ def _detach_params(module: nn.Module, layout: Layout) -> None:
         _set_param_data(module, name, torch.empty(0, dtype=dtype))
 
 
+class _ResidencyStates(Mapping):
+    """Read-only ``block_id -> state string`` view handed to the policy (looked up on demand)."""
+
+    def __init__(self, residency: "ResidencyMap", block_ids: list[str]) -> None:
+        self._residency, self._ids = residency, block_ids
+
+    def __getitem__(self, block_id: str) -> str:
+        return self._residency.get_state(block_id).value
+
+    def __iter__(self):
+        return iter(self._ids)
+
+    def __len__(self) -> int:
+        return len(self._ids)
+
+
 class StagehandScheduler:
     def __init__(self, registry: "BlockRegistry", residency: "ResidencyMap", transfer_engine: "AsyncTransferEngine",
                  budget: BudgetLike, policy: StaticLookaheadPolicy, guards: GuardsLike | None,
@@ -187,6 +204,8 @@ class StagehandScheduler:
         self._ordered_blocks = self._registry.blocks_in_order()
         self._total_blocks = len(self._ordered_blocks)
         self._order_to_id = {e.exec_order: e.block_id for e in self._ordered_blocks}
+        self._block_ids = [e.block_id for e in self._ordered_blocks]
+        self._view_cache: dict[tuple[str, int], list[tuple[Any, str, torch.Tensor]]] = {}
         if getattr(self, "_image_plans", None):
             self._image_plans.clear()
 
@@ -387,7 +406,7 @@ class StagehandScheduler:
     # ── prefetch ─────────────────────────────────────────────────────
 
     def _prefetch_ahead(self) -> None:
-        states = {e.block_id: self._residency.get_state(e.block_id).value for e in self._ordered_blocks}
+        states = _ResidencyStates(self._residency, self._block_ids)
         for idx in self._policy.blocks_to_prefetch(self._cursor - 1, self._total_blocks, states):
             if idx >= self._total_blocks:
                 break
@@ -444,7 +463,8 @@ class StagehandScheduler:
         device = torch.device("cuda", torch.cuda.current_device())
         n_staging = self._config.device_staging_slabs or (self._policy.prefetch_window + 1)
         self._streamer = Int8BlockStreamer(device, self._engine.copy_stream, n_staging)
-        self._device_pool = DeviceSlabPool(device)
+        self._device_pool = DeviceSlabPool(device, on_allocation=getattr(self._budget, "invalidate", None),
+                                           on_trim=self._view_cache.clear)
         if hasattr(self._budget, "set_reusable_bytes_source"):
             self._budget.set_reusable_bytes_source(self._device_pool.reusable_bytes)
         self._image_store = ImageStore(self._image_cache_budget(), pinned=True)
@@ -661,7 +681,10 @@ class StagehandScheduler:
         res = self._residency.get_entry(block_id)
         module = entry.module_ref()
         if module is not None and res.param_layout is not None and res.gpu_tensor is not None:
-            _restore_params_from_tensor(module, res.gpu_tensor.view(torch.uint8), res.param_layout)
+            if res.device_slab is not None:
+                self._restore_from_pooled_slab(block_id, module, res)
+            else:
+                _restore_params_from_tensor(module, res.gpu_tensor.view(torch.uint8), res.param_layout)
             target = res.gpu_tensor.device
             for param in module.parameters():
                 if param.grad is not None and param.grad.device != target:
@@ -669,6 +692,30 @@ class StagehandScheduler:
         if res.host_slab is not None and not isinstance(res.host_slab, tuple):
             self._engine._pool.release(res.host_slab)
         res.host_slab = None
+
+    def _restore_from_pooled_slab(self, block_id: str, module: nn.Module, res: "ResidencyEntry") -> None:
+        """Repoint the parameters at views of a pooled slab; the views are built once per (block, slab).
+
+        Slabs are recycled, so the same block meets the same few slabs again and again; reusing the
+        view tensors turns a reload's repointing into one attribute assignment per parameter.
+        """
+        key = (block_id, res.device_slab.slab_id)
+        cached = self._view_cache.get(key)
+        if cached is None:
+            flat = res.gpu_tensor.view(torch.uint8)
+            cached = []
+            for name, shape, dtype, offset, numel in res.param_layout:
+                owner, leaf = _resolve(module, name)
+                cached.append((owner, leaf, flat[offset : offset + numel * dtype.itemsize].view(dtype).reshape(shape)))
+            if len(self._view_cache) > 4096:
+                self._view_cache.clear()
+            self._view_cache[key] = cached
+        for owner, leaf, view in cached:
+            param = getattr(owner, leaf)
+            try:
+                param.data = view
+            except RuntimeError:
+                setattr(owner, leaf, nn.Parameter(view, requires_grad=param.requires_grad))
 
     # ── eviction ─────────────────────────────────────────────────────
 

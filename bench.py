@@ -476,6 +476,8 @@ def main() -> None:
             out["vram_pool"] = {"allocations": rt._scheduler._device_pool.allocations,
                                 "reuses": rt._scheduler._device_pool.reuses}
             rt.shutdown()
+            torch.cuda.synchronize()
+            barrier(dist_state)          # no rank frees its arena while a peer may still be reading it
             if store is not None:
                 store.close()
             del model, rt

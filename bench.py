@@ -52,6 +52,8 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--shapes", default="", help="kernel_sweep: comma-separated NxK list (default: the full sweep)")
     ap.add_argument("--prefetch-k", type=int, default=3)
     ap.add_argument("--vram-budget-gb", type=float, default=8.0)
+    ap.add_argument("--layout", default="striped", choices=["striped", "owner"],
+                    help="multi-GPU: rows of every weight striped over all ranks, or whole blocks round-robin")
     ap.add_argument("--no-fused", action="store_true", help="multi-GPU: copy-engine pull + kernel instead of the fused kernel")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--skip-delivery-only", action="store_true")
@@ -443,7 +445,8 @@ def main() -> None:
             if source == "hbm":
                 from stagehand_b200.sharded import DeviceImageStore
 
-                store = DeviceImageStore(rt, rank=rank, world=world, fused=not args.no_fused)
+                store = DeviceImageStore(rt, rank=rank, world=world, fused=not args.no_fused,
+                                         layout=args.layout if world > 1 else "owner")
             device_inputs = [t.cuda() for t in host_inputs]
             host_io = name == "e2e"
             step = [0]
@@ -526,8 +529,9 @@ def compose_line(args, world: int, results: dict, peaks: dict, link_peak: float,
                    "prefetch_k": args.prefetch_k, "int8_elements_per_forward": v["desc"]["int8_elements"],
                    "l2": "inputs larger than L2 (11.8 GB of INT8 per step); no flush",
                    "value_source": "INT8 images resident in HBM" + ("" if world == 1 else
-                                   f", sharded round-robin over {world} GPUs, " +
-                                   ("fused peer-load dequant" if not args.no_fused else "copy-engine pull + dequant")),
+                                   f", {args.layout} layout over {world} GPUs, " +
+                                   ("fused peer-load dequant" if (not args.no_fused or args.layout == "striped")
+                                    else "copy-engine pull + dequant")),
                    "e2e_source": "packed INT8 images in page-locked host memory" if world == 1 else
                                  "sharded HBM images; host inputs copied in, scalar read back each step",
                    "weights": "shared per shape in the slab file" if not args.unique_weights else "unique per layer"},

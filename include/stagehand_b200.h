@@ -49,6 +49,9 @@ extern "C" {
 
 /* descriptor flags */
 #define SH_DESC_PEER_SOURCE   1u  /* source bytes live in another GPU's memory: plain loads only */
+#define SH_DESC_ABSOLUTE      2u  /* src_off / scale_off / zp_off are absolute device addresses (a stripe of the
+                                     matrix resident in some GPU's arena), not offsets into the packed image; the
+                                     caller vouches for their extent -- only alignment is checked */
 
 /*
  * One parameter of a block.  All *_off fields are byte offsets: sources from

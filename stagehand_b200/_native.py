@@ -14,7 +14,7 @@ from stagehand_b200.errors import StagehandOOMError, TransferError
 __all__ = [
     "ShParamDesc", "ShDeviceInfo", "ShStats", "lib", "is_built", "check", "LIB_PATH", "EXPORTED_SYMBOLS",
     "SH_KIND_DEQUANT_I8", "SH_KIND_CAST_F32", "SH_KIND_COPY", "SH_KIND_ZERO",
-    "SH_DT_BF16", "SH_DT_F16", "SH_DT_F32", "SH_DESC_PEER_SOURCE",
+    "SH_DT_BF16", "SH_DT_F16", "SH_DT_F32", "SH_DESC_PEER_SOURCE", "SH_DESC_ABSOLUTE",
     "SH_OK", "SH_ERR_INVALID_ARG", "SH_ERR_OOM", "SH_ERR_CUDA", "SH_ERR_TIMEOUT", "SH_ERR_BUSY", "SH_ERR_UNSUPPORTED",
 ]
 
@@ -24,6 +24,7 @@ SH_OK, SH_ERR_INVALID_ARG, SH_ERR_OOM, SH_ERR_CUDA, SH_ERR_TIMEOUT, SH_ERR_BUSY,
 SH_KIND_DEQUANT_I8, SH_KIND_CAST_F32, SH_KIND_COPY, SH_KIND_ZERO = 0, 1, 2, 3
 SH_DT_BF16, SH_DT_F16, SH_DT_F32 = 0, 1, 2
 SH_DESC_PEER_SOURCE = 1
+SH_DESC_ABSOLUTE = 2
 SH_NOALLOC_MAX_BYTES = 32 * 1024 * 1024
 
 

@@ -457,6 +457,7 @@ int build_plans(const ShParamDesc* descs, int n, const void* packed, size_t pack
         DescDev D;
         memset(&D, 0, sizeof(D));
         D.flags = u.flags & SH_DESC_PEER_SOURCE;
+        const bool absolute = (u.flags & SH_DESC_ABSOLUTE) != 0;
         int64_t dst_bytes = 0, n_tiles = 0;
 #define SQ_FAIL(...)                                      \
     do {                                                  \
@@ -468,16 +469,24 @@ int build_plans(const ShParamDesc* descs, int n, const void* packed, size_t pack
             case SH_KIND_DEQUANT_I8: {
                 if (u.rows <= 0 || u.cols <= 0 || u.ld < u.cols) SQ_FAIL("descriptor %d: bad rows/cols/ld", i);
                 if (u.rows > (int64_t(1) << 40) / u.cols) SQ_FAIL("descriptor %d: matrix too large", i);
-                if (u.src_off < 0 || u.src_off + (u.rows - 1) * u.ld + u.cols > pbytes)
-                    SQ_FAIL("descriptor %d: int8 rows outside the packed image", i);
-                if (u.scale_off < 0 || u.scale_off % 4 != 0 || u.scale_off + u.rows * 4 > pbytes)
-                    SQ_FAIL("descriptor %d: scales outside the packed image or not 4-byte aligned", i);
-                if (u.zp_off >= 0 && (u.zp_off % 4 != 0 || u.zp_off + u.rows * 4 > pbytes))
-                    SQ_FAIL("descriptor %d: zero points outside the packed image or not 4-byte aligned", i);
+                if (absolute) {
+                    if (u.src_off <= 0 || u.scale_off <= 0 || u.zp_off == 0)
+                        SQ_FAIL("descriptor %d: null absolute source address", i);
+                    D.src = reinterpret_cast<const uint8_t*>(static_cast<uintptr_t>(u.src_off));
+                    D.scale = reinterpret_cast<const float*>(static_cast<uintptr_t>(u.scale_off));
+                    D.zp = u.zp_off > 0 ? reinterpret_cast<const float*>(static_cast<uintptr_t>(u.zp_off)) : nullptr;
+                } else {
+                    if (u.src_off < 0 || u.src_off + (u.rows - 1) * u.ld + u.cols > pbytes)
+                        SQ_FAIL("descriptor %d: int8 rows outside the packed image", i);
+                    if (u.scale_off < 0 || u.scale_off % 4 != 0 || u.scale_off + u.rows * 4 > pbytes)
+                        SQ_FAIL("descriptor %d: scales outside the packed image or not 4-byte aligned", i);
+                    if (u.zp_off >= 0 && (u.zp_off % 4 != 0 || u.zp_off + u.rows * 4 > pbytes))
+                        SQ_FAIL("descriptor %d: zero points outside the packed image or not 4-byte aligned", i);
+                    D.src = pbase + u.src_off;
+                    D.scale = reinterpret_cast<const float*>(pbase + u.scale_off);
+                    D.zp = u.zp_off >= 0 ? reinterpret_cast<const float*>(pbase + u.zp_off) : nullptr;
+                }
                 dst_bytes = u.rows * u.cols * osz;
-                D.src = pbase + u.src_off;
-                D.scale = reinterpret_cast<const float*>(pbase + u.scale_off);
-                D.zp = u.zp_off >= 0 ? reinterpret_cast<const float*>(pbase + u.zp_off) : nullptr;
                 if (!aligned(D.scale, 4) || (D.zp && !aligned(D.zp, 4)))
                     SQ_FAIL("descriptor %d: scale pointer not 4-byte aligned", i);
                 D.rows = u.rows; D.cols = u.cols; D.ld = u.ld;
@@ -489,7 +498,7 @@ int build_plans(const ShParamDesc* descs, int n, const void* packed, size_t pack
                     n_tiles = ceil_div(u.rows * D.segs_per_row, kTileSegs);
                     // bulk scale fetch: 16-byte aligned arrays whose 4-row padding stays inside the image
                     const int64_t rows4 = (u.rows + 3) & ~int64_t(3);
-                    const bool bulk_ok = !(D.flags & SH_DESC_PEER_SOURCE) && aligned(D.scale, 16) &&
+                    const bool bulk_ok = !absolute && !(D.flags & SH_DESC_PEER_SOURCE) && aligned(D.scale, 16) &&
                                          u.scale_off + rows4 * 4 <= pbytes &&
                                          (D.zp == nullptr || (aligned(D.zp, 16) && u.zp_off + rows4 * 4 <= pbytes));
                     if (bulk_ok) D.flags |= kFlagBulkScales;
@@ -507,10 +516,11 @@ int build_plans(const ShParamDesc* descs, int n, const void* packed, size_t pack
             }
             case SH_KIND_CAST_F32: {
                 if (u.cols < 0) SQ_FAIL("descriptor %d: negative count", i);
-                if (u.src_off < 0 || u.src_off % 4 != 0 || u.src_off + u.cols * 4 > pbytes)
+                if (!absolute && (u.src_off < 0 || u.src_off % 4 != 0 || u.src_off + u.cols * 4 > pbytes))
                     SQ_FAIL("descriptor %d: fp32 source outside the packed image or not 4-byte aligned", i);
+                if (absolute && u.src_off <= 0) SQ_FAIL("descriptor %d: null absolute source address", i);
                 dst_bytes = u.cols * osz;
-                D.src = pbase + u.src_off;
+                D.src = absolute ? reinterpret_cast<const uint8_t*>(static_cast<uintptr_t>(u.src_off)) : pbase + u.src_off;
                 if (!aligned(D.src, 4)) SQ_FAIL("descriptor %d: fp32 source pointer not 4-byte aligned", i);
                 D.rows = 1; D.cols = u.cols;
                 const bool vec = (u.cols % 4 == 0) && aligned(D.src, 16) && aligned(obase + u.dst_off, 4 * osz);
@@ -523,10 +533,12 @@ int build_plans(const ShParamDesc* descs, int n, const void* packed, size_t pack
             case SH_KIND_ZERO: {
                 if (u.cols < 0) SQ_FAIL("descriptor %d: negative byte count", i);
                 const bool zero = u.kind == SH_KIND_ZERO;
-                if (!zero && (u.src_off < 0 || u.src_off + u.cols > pbytes))
+                if (!zero && !absolute && (u.src_off < 0 || u.src_off + u.cols > pbytes))
                     SQ_FAIL("descriptor %d: copy source outside the packed image", i);
+                if (!zero && absolute && u.src_off <= 0) SQ_FAIL("descriptor %d: null absolute source address", i);
                 dst_bytes = u.cols;
-                D.src = zero ? nullptr : pbase + u.src_off;
+                D.src = zero ? nullptr
+                             : (absolute ? reinterpret_cast<const uint8_t*>(static_cast<uintptr_t>(u.src_off)) : pbase + u.src_off);
                 D.rows = 1; D.cols = u.cols;
                 const bool vec = (u.cols % 16 == 0) && aligned(obase + u.dst_off, 16) && (zero || aligned(D.src, 16));
                 D.path = zero ? (vec ? kPathZeroVec : kPathZeroScalar) : (vec ? kPathCopyVec : kPathCopyScalar);

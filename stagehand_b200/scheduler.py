@@ -193,7 +193,7 @@ class StagehandScheduler:
         self._device_pool: Any = None
         self._image_store: Any = None
         self._image_plans: dict[str, "PackedBlockImage"] = {}
-        self._device_sources: dict[str, tuple[int, bool]] = {}      # block_id -> (device ptr of static section, is_peer)
+        self._device_sources: dict[str, Any] = {}                   # block_id -> streamer.DeviceSource
         self._device_source_fused = True
         self._deferred_slabs: list[tuple[Any, "PinnedSlab"]] = []   # (copied event, pool slab) awaiting DMA completion
         self._squareq_v2_loader: Any = None
@@ -556,8 +556,7 @@ class StagehandScheduler:
         if device_src is None:
             ticket = self._streamer.submit_from_host(plan, image, out_slab)
         else:
-            ticket = self._streamer.submit_from_device(plan, device_src[0], device_src[1], self._device_source_fused,
-                                                       image, out_slab)
+            ticket = self._streamer.submit_from_device(plan, device_src, self._device_source_fused, image, out_slab)
         ticket.host_slab = slab
         res.host_slab = None
         res.device_slab = out_slab
@@ -582,8 +581,8 @@ class StagehandScheduler:
                              base_offset=plan.static_bytes)
         return image, None
 
-    def set_device_sources(self, sources: dict[str, tuple[int, bool]], fused: bool = True) -> None:
-        """Declare blocks whose static INT8 image is resident in HBM: ``block_id -> (pointer, is_peer)``.
+    def set_device_sources(self, sources: dict[str, Any], fused: bool = True) -> None:
+        """Declare blocks whose static INT8 image is resident in HBM: ``block_id -> DeviceSource``.
 
         With *fused* the block kernel reads the image in place (plain loads over NVLink
         for a peer); otherwise it is pulled into a local staging slab by a copy engine first.

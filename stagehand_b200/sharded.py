@@ -3,18 +3,20 @@
 The reference is single-GPU and always sources a block from host memory.  Here the
 static section of every block's packed image can live in device memory instead:
 
-* ``world == 1``: all images are parked in this GPU's HBM (no host-link traffic
-  on the steady path; the block kernel reads them in place);
-* ``world > 1``: block *i* is owned by rank ``i % world`` (``layout="owner"``), or
-  every block's rows are striped over all ranks (``layout="striped"``, balanced
-  NVLink egress).  Owners export their arena with CUDA IPC; consumers map it and
-  either read it directly from the block kernel (``fused=True``: plain peer loads,
-  gather and dequant in one kernel) or pull it into a local staging slab with a
-  copy engine first (``fused=False``).
+* ``world == 1``: all images are parked in this GPU's HBM (no host-link traffic on the
+  steady path; the block kernel reads them in place);
+* ``layout="owner"``: block *i* lives whole in the arena of rank ``i % world``.  Consumers
+  read it in place from the block kernel (``fused=True``: plain peer loads, gather and
+  dequant in one kernel) or pull it into a local staging slab with a copy engine first;
+* ``layout="striped"``: the rows of every weight matrix are cut into ``world`` stripes, one
+  per rank, so that a block load reads 1/world of its bytes from every GPU -- NVLink egress
+  stays balanced even when all ranks want the same block at the same moment.  Always fused:
+  the consumer's descriptors carry absolute addresses into the ranks' arenas.
 
-There is no data-path collective: each rank runs its own forward and pulls what it
-needs.  ``torch.distributed`` is used once, at set-up, to exchange the 64-byte IPC
-handles.  The planning functions are pure (tested on CPU ranks over gloo).
+Arenas are allocated with ``sh_device_alloc`` and exported with CUDA IPC; the 64-byte handles
+are exchanged once with ``all_gather_object``.  There is no data-path collective: each rank
+runs its own forward and reads what it needs.  The planning functions are pure (tested on
+CPU ranks over gloo).
 """
 from __future__ import annotations
 
@@ -25,11 +27,21 @@ from typing import Any, Sequence
 import torch
 
 from stagehand_b200 import _native
+from stagehand_b200._native import (SH_DESC_ABSOLUTE, SH_DESC_PEER_SOURCE, SH_KIND_DEQUANT_I8, SH_KIND_ZERO,
+                                    ShParamDesc)
 from stagehand_b200.errors import TransferError
 
-__all__ = ["ShardPlan", "plan_shards", "DeviceImageStore", "park_images_in_hbm", "shard_images_over_ranks"]
+__all__ = ["ShardPlan", "plan_shards", "StripePiece", "StripeDesc", "BlockStripes", "plan_block_stripes",
+           "DeviceImageStore", "park_images_in_hbm", "shard_images_over_ranks"]
 
 _ALIGN = 4096
+
+
+def _up(value: int, multiple: int) -> int:
+    return -(-int(value) // multiple) * multiple
+
+
+# ── owner layout ─────────────────────────────────────────────────────────
 
 
 @dataclass
@@ -56,61 +68,181 @@ def plan_shards(block_bytes: Sequence[tuple[str, int]], world: int, layout: str 
         owner = index % world
         offset = plan.arena_bytes[owner]
         plan.placement[block_id] = (owner, offset, int(nbytes))
-        plan.arena_bytes[owner] = offset + -(-int(nbytes) // _ALIGN) * _ALIGN
+        plan.arena_bytes[owner] = offset + _up(nbytes, _ALIGN)
     return plan
 
 
+# ── striped layout ───────────────────────────────────────────────────────
+
+
+@dataclass
+class StripePiece:
+    """A byte range of a block's full static image that is stored in *rank*'s arena."""
+
+    rank: int
+    full_off: int
+    nbytes: int
+    arena_off: int
+
+
+@dataclass
+class StripeDesc:
+    """One descriptor of the consumer's striped view; source offsets are relative to *rank*'s arena."""
+
+    kind: int
+    rank: int
+    src_off: int
+    scale_off: int
+    zp_off: int          # -1: no zero points
+    dst_off: int
+    rows: int
+    cols: int
+    ld: int
+
+
+@dataclass
+class BlockStripes:
+    pieces: list[StripePiece] = field(default_factory=list)
+    descs: list[StripeDesc] = field(default_factory=list)
+
+
+def stripe_bounds(rows: int, world: int) -> list[int]:
+    """Row boundaries ``b[0]=0 <= ... <= b[world]=rows``; inner ones are multiples of 4 (16-byte scale slices)."""
+    inner = [min(rows, (rows * r // world) // 4 * 4) for r in range(1, world)]
+    return [0, *inner, rows]
+
+
+def plan_block_stripes(static_descs: Sequence[Any], itemsize: int, world: int, home_rank: int,
+                       arena_cursor: list[int]) -> BlockStripes:
+    """Cut one block's static descriptors into per-rank stripes and place them in the arenas.
+
+    *static_descs* are the block's image-relative descriptors (dense int8 rows).  Weight rows are cut
+    at :func:`stripe_bounds`; bias / copy vectors go whole to *home_rank*.  *arena_cursor* holds the next
+    free byte of every rank's arena and is advanced in place (each block starts 4 KiB aligned).
+    """
+    out = BlockStripes()
+    for r in range(world):
+        arena_cursor[r] = _up(arena_cursor[r], _ALIGN)
+
+    def place(rank: int, full_off: int, nbytes: int, align: int, reserve: int | None = None) -> int:
+        at = _up(arena_cursor[rank], align)
+        out.pieces.append(StripePiece(rank, int(full_off), int(nbytes), at))
+        arena_cursor[rank] = at + int(reserve if reserve is not None else nbytes)
+        return at
+
+    for d in static_descs:
+        if d.kind == SH_KIND_DEQUANT_I8:
+            rows, cols, ld = int(d.rows), int(d.cols), int(d.ld)
+            bounds = stripe_bounds(rows, world)
+            for r in range(world):
+                r0, r1 = bounds[r], bounds[r + 1]
+                n = r1 - r0
+                if n <= 0:
+                    continue
+                src = place(r, d.src_off + r0 * ld, (n - 1) * ld + cols, 256)
+                scale = place(r, d.scale_off + r0 * 4, n * 4, 16, reserve=_up(n, 4) * 4)
+                zp = place(r, d.zp_off + r0 * 4, n * 4, 16, reserve=_up(n, 4) * 4) if d.zp_off >= 0 else -1
+                out.descs.append(StripeDesc(SH_KIND_DEQUANT_I8, r, src, scale, zp, int(d.dst_off) + r0 * cols * itemsize,
+                                            n, cols, ld))
+        elif d.kind == SH_KIND_ZERO:
+            out.descs.append(StripeDesc(SH_KIND_ZERO, home_rank, 0, 0, -1, int(d.dst_off), 1, int(d.cols), 0))
+        else:   # CAST_F32 (cols fp32 values) or COPY (cols bytes): whole vector on the home rank
+            nbytes = int(d.cols) * (4 if d.kind == _native.SH_KIND_CAST_F32 else 1)
+            src = place(home_rank, d.src_off, nbytes, 16, reserve=_up(nbytes, 16))
+            out.descs.append(StripeDesc(int(d.kind), home_rank, src, 0, -1, int(d.dst_off), 1, int(d.cols), 0))
+    return out
+
+
+# ── the store ────────────────────────────────────────────────────────────
+
+
 class DeviceImageStore:
-    """Arena of INT8 static images in this rank's HBM plus mappings of the peers' arenas."""
+    """This rank's arena of INT8 static images (or stripes) plus mappings of the peers' arenas.
+
+    With *emulate_world* > 1 a single process plays every rank on its one GPU: it allocates and
+    fills all the arenas locally and treats the others as peers (plain-load path included).  That is
+    how the sharded layouts are exercised where fewer GPUs than ranks are available.
+    """
 
     def __init__(self, runtime: Any, rank: int = 0, world: int = 1, layout: str = "owner", fused: bool = True,
-                 group: Any = None) -> None:
+                 group: Any = None, emulate_world: int = 0) -> None:
         if not torch.cuda.is_available():
             raise TransferError("device-resident images need a CUDA device")
+        if layout not in ("owner", "striped"):
+            raise ValueError(f"unknown shard layout {layout!r}")
         self._lib = _native.lib()
-        self.rank, self.world, self.fused = rank, world, fused
+        self._emulated = emulate_world > 1
+        if self._emulated:
+            rank, world = 0, emulate_world
+        self.rank, self.world, self.fused, self.layout = rank, world, fused, layout
         self._runtime = runtime
         sched = runtime._scheduler
         sched._ensure_int8_path()
-        entries = [e for e in runtime._registry.blocks_in_order() if e.squareq_backed]
-        plans = {e.block_id: sched._image_plan(e) for e in entries}
-        self.plan = plan_shards([(e.block_id, plans[e.block_id].static_bytes) for e in entries], world, layout)
+        self._entries = [e for e in runtime._registry.blocks_in_order() if e.squareq_backed]
+        self._plans = {e.block_id: sched._image_plan(e) for e in self._entries}
+        self._arenas: dict[int, int] = {}          # rank -> base pointer valid in this process
+        self._owned: list[int] = []                # base pointers this process allocated
+        self._opened: list[int] = []               # base pointers mapped from peers
 
-        self._arena = ctypes.c_void_p(0)
-        self._peer_ptrs: dict[int, int] = {}
-        my_bytes = max(self.plan.arena_bytes[rank], _ALIGN)
-        _native.check(self._lib.sh_device_alloc(my_bytes, ctypes.byref(self._arena)), "sh_device_alloc")
-        self._fill_arena(entries, plans)
-        self._exchange_handles(group)
+        if layout == "owner":
+            self.plan = plan_shards([(e.block_id, self._plans[e.block_id].static_bytes) for e in self._entries], world)
+            self.arena_bytes = list(self.plan.arena_bytes)
+            copies = self._owner_copies()
+        else:
+            self.stripes, self.arena_bytes = self._plan_all_stripes()
+            copies = {bid: bs.pieces for bid, bs in self.stripes.items()}
 
-        sources: dict[str, tuple[int, bool]] = {}
-        for block_id, (owner, offset, _n) in self.plan.placement.items():
-            base = self._arena.value if owner == rank else self._peer_ptrs[owner]
-            sources[block_id] = (int(base) + offset, owner != rank)
-        sched.set_device_sources(sources, fused=fused)
-        largest_dyn = max((p.total_bytes - p.static_bytes for p in plans.values()), default=0)
-        largest = max((p.total_bytes for p in plans.values()), default=_ALIGN)
+        local_ranks = range(world) if self._emulated else [rank]
+        for r in local_ranks:
+            ptr = ctypes.c_void_p(0)
+            _native.check(self._lib.sh_device_alloc(max(self.arena_bytes[r], _ALIGN), ctypes.byref(ptr)), "sh_device_alloc")
+            self._arenas[r] = int(ptr.value)
+            self._owned.append(int(ptr.value))
+        self._fill(copies, set(local_ranks))
+        if not self._emulated:
+            self._exchange_handles(group)
+
+        sched.set_device_sources(self._sources(), fused=fused or layout == "striped")
+        largest_dyn = max((p.total_bytes - p.static_bytes for p in self._plans.values()), default=0)
+        largest = max((p.total_bytes for p in self._plans.values()), default=_ALIGN)
         sched._streamer.ensure_staging(largest, largest_dyn)
 
-    def _fill_arena(self, entries, plans) -> None:
-        """Pack each owned block once into a temporary pinned buffer and copy its static section into the arena."""
-        owned = [e for e in entries if self.plan.placement[e.block_id][0] == self.rank]
-        if not owned:
+    # ── planning ─────────────────────────────────────────────────────
+
+    def _owner_copies(self) -> dict[str, list[StripePiece]]:
+        return {bid: [StripePiece(owner, 0, nbytes, offset)] for bid, (owner, offset, nbytes) in self.plan.placement.items()}
+
+    def _plan_all_stripes(self) -> tuple[dict[str, BlockStripes], list[int]]:
+        cursor = [0] * self.world
+        stripes: dict[str, BlockStripes] = {}
+        for index, e in enumerate(self._entries):
+            plan = self._plans[e.block_id]
+            static_descs, n_static, _d, _n = plan.split_descs()
+            stripes[e.block_id] = plan_block_stripes([static_descs[i] for i in range(n_static)],
+                                                     plan.runtime_dtype.itemsize, self.world, index % self.world, cursor)
+        return stripes, [_up(c, _ALIGN) for c in cursor]
+
+    # ── filling and mapping ──────────────────────────────────────────
+
+    def _fill(self, copies: dict[str, list[StripePiece]], local_ranks: set[int]) -> None:
+        """Pack each block once into a temporary pinned buffer and copy the locally stored pieces into the arenas."""
+        todo = [(e, [p for p in copies[e.block_id] if p.rank in local_ranks and p.nbytes > 0]) for e in self._entries]
+        todo = [(e, pieces) for e, pieces in todo if pieces]
+        if not todo:
             return
-        largest = max(plans[e.block_id].total_bytes for e in owned)
+        largest = max(self._plans[e.block_id].total_bytes for e, _ in todo)
         tmp = ctypes.c_void_p(0)
         _native.check(self._lib.sh_host_alloc(largest, ctypes.byref(tmp)), "sh_host_alloc")
         try:
             buf = torch.frombuffer((ctypes.c_uint8 * largest).from_address(tmp.value), dtype=torch.uint8)
-            stream = torch.cuda.current_stream()
+            stream = torch.cuda.current_stream().cuda_stream
             threads = int(getattr(self._runtime._config, "pack_threads", 8))
-            for e in owned:
-                plan = plans[e.block_id]
-                _owner, offset, nbytes = self.plan.placement[e.block_id]
-                plan.fill_static(buf, threads=threads)
-                _native.check(self._lib.sh_copy_h2d_async(self._arena.value + offset, tmp.value, nbytes,
-                                                          stream.cuda_stream), "sh_copy_h2d_async")
-                _native.check(self._lib.sh_stream_synchronize(stream.cuda_stream, 120_000), "sh_stream_synchronize")
+            for e, pieces in todo:
+                self._plans[e.block_id].fill_static(buf, threads=threads)
+                for p in pieces:
+                    _native.check(self._lib.sh_copy_h2d_async(self._arenas[p.rank] + p.arena_off, tmp.value + p.full_off,
+                                                              p.nbytes, stream), "sh_copy_h2d_async")
+                _native.check(self._lib.sh_stream_synchronize(stream, 120_000), "sh_stream_synchronize")
             del buf
         finally:
             self._lib.sh_host_free(tmp)
@@ -121,28 +253,57 @@ class DeviceImageStore:
         import torch.distributed as dist
 
         handle = (ctypes.c_uint8 * 64)()
-        _native.check(self._lib.sh_ipc_export(self._arena, handle), "sh_ipc_export")
+        _native.check(self._lib.sh_ipc_export(self._arenas[self.rank], handle), "sh_ipc_export")
         gathered: list[Any] = [None] * self.world
         dist.all_gather_object(gathered, bytes(handle), group=group)
         for peer, raw in enumerate(gathered):
-            if peer == self.rank or self.plan.arena_bytes[peer] == 0:
+            if peer == self.rank or self.arena_bytes[peer] == 0:
                 continue
             peer_handle = (ctypes.c_uint8 * 64).from_buffer_copy(raw)
             ptr = ctypes.c_void_p(0)
             _native.check(self._lib.sh_ipc_open(peer_handle, ctypes.byref(ptr)), f"sh_ipc_open(rank {peer})")
-            self._peer_ptrs[peer] = int(ptr.value)
+            self._arenas[peer] = int(ptr.value)
+            self._opened.append(int(ptr.value))
+
+    # ── what the scheduler is told ───────────────────────────────────
+
+    def _sources(self) -> dict[str, Any]:
+        from stagehand_b200.streamer import DeviceSource
+
+        sources: dict[str, Any] = {}
+        if self.layout == "owner":
+            for block_id, (owner, offset, nbytes) in self.plan.placement.items():
+                remote = owner != self.rank
+                sources[block_id] = DeviceSource(ptr=self._arenas[owner] + offset, is_peer=remote, span_bytes=nbytes,
+                                                 peer_bytes=nbytes if remote else 0)
+            return sources
+        for block_id, bs in self.stripes.items():
+            rows = []
+            for d in bs.descs:
+                base = self._arenas.get(d.rank, 0)
+                flags = 0 if d.kind == SH_KIND_ZERO else SH_DESC_ABSOLUTE | (SH_DESC_PEER_SOURCE if d.rank != self.rank else 0)
+                rows.append(ShParamDesc(
+                    kind=d.kind, flags=flags, src_off=base + d.src_off if flags else 0,
+                    scale_off=base + d.scale_off if d.kind == SH_KIND_DEQUANT_I8 else 0,
+                    zp_off=(base + d.zp_off) if d.zp_off >= 0 else -1, dst_off=d.dst_off, rows=d.rows, cols=d.cols, ld=d.ld))
+            remote_bytes = sum(p.nbytes for p in bs.pieces if p.rank != self.rank)
+            sources[block_id] = DeviceSource(ptr=self._arenas[self.rank], is_peer=False, descs=_native.make_descs(rows),
+                                             n_descs=len(rows), span_bytes=max(self.arena_bytes[self.rank], _ALIGN),
+                                             peer_bytes=remote_bytes)
+        return sources
 
     def resident_bytes(self) -> int:
-        return self.plan.arena_bytes[self.rank]
+        return sum(self.arena_bytes[r] for r in (range(self.world) if self._emulated else [self.rank]))
 
     def close(self) -> None:
-        """Unmap the peers' arenas and free this rank's.  Call after the runtime has shut down."""
-        for ptr in self._peer_ptrs.values():
+        """Unmap the peers' arenas and free this process's.  Call after the runtime has shut down."""
+        for ptr in self._opened:
             self._lib.sh_ipc_close(ptr)
-        self._peer_ptrs.clear()
-        if self._arena.value:
-            self._lib.sh_device_free(self._arena)
-            self._arena = ctypes.c_void_p(0)
+        self._opened.clear()
+        for ptr in self._owned:
+            self._lib.sh_device_free(ptr)
+        self._owned.clear()
+        self._arenas.clear()
 
 
 def park_images_in_hbm(runtime: Any, fused: bool = True) -> DeviceImageStore:
@@ -150,7 +311,7 @@ def park_images_in_hbm(runtime: Any, fused: bool = True) -> DeviceImageStore:
     return DeviceImageStore(runtime, rank=0, world=1, fused=fused)
 
 
-def shard_images_over_ranks(runtime: Any, fused: bool = True, layout: str = "owner", group: Any = None) -> DeviceImageStore:
+def shard_images_over_ranks(runtime: Any, fused: bool = True, layout: str = "striped", group: Any = None) -> DeviceImageStore:
     """One process per GPU: shard the INT8 images over the ranks of *group* (default: the world group)."""
     import torch.distributed as dist
 

@@ -28,7 +28,7 @@ from stagehand_b200.errors import StagehandOOMError, TransferError
 from stagehand_b200.events import Event, acquire_event, release_event, stream_handle
 from stagehand_b200.packed import PackedBlockImage
 
-__all__ = ["HostImage", "ImageStore", "StreamTicket", "Int8BlockStreamer"]
+__all__ = ["HostImage", "ImageStore", "DeviceSource", "StreamTicket", "Int8BlockStreamer"]
 
 
 @dataclass
@@ -106,6 +106,23 @@ class ImageStore:
     def close(self) -> None:
         for block_id in list(self._images):
             self.drop(block_id)
+
+
+@dataclass
+class DeviceSource:
+    """Where the static section of a block's image is resident in device memory.
+
+    Either one contiguous image at *ptr* (this GPU's HBM, or a peer's when *is_peer*), expanded with the
+    block's own descriptors, or -- when *descs* is given -- a set of row stripes spread over several GPUs'
+    arenas, described by absolute-address descriptors built once for this consumer.
+    """
+
+    ptr: int
+    is_peer: bool = False
+    descs: Any = None             # ctypes array of ShParamDesc with SH_DESC_ABSOLUTE set
+    n_descs: int = 0
+    span_bytes: int = 0           # bytes addressable from ptr (bounds for non-absolute descriptors)
+    peer_bytes: int = 0           # bytes this consumer reads from other GPUs per load
 
 
 @dataclass
@@ -189,7 +206,7 @@ class Int8BlockStreamer:
         launches = -(-image.n_descs // 32)
         return StreamTicket(image.block_id, ready, copied, link_bytes=image.total_bytes, launches=launches)
 
-    def submit_from_device(self, image: PackedBlockImage, src_ptr: int, src_is_peer: bool, fused: bool,
+    def submit_from_device(self, image: PackedBlockImage, source: DeviceSource, fused: bool,
                            dynamic_host: HostImage | None, out_slab: DeviceSlab) -> StreamTicket:
         """Image whose static section is resident in HBM (this GPU's, or a peer's over NVLink).
 
@@ -201,12 +218,18 @@ class Int8BlockStreamer:
         (*dynamic_host* holds that section only).
         """
         static_descs, n_static, dyn_descs, n_dyn = image.split_descs()
+        src_ptr, src_is_peer = source.ptr, source.is_peer
+        static_bytes = image.static_bytes
         self._order_output(out_slab)
         copied: Event | None = None
         peer_bytes = 0
         launches = 0
         dq = stream_handle(self.dequant_stream)
-        if fused:
+        if source.descs is not None:
+            # striped over several arenas: the consumer's absolute-address descriptors, always fused
+            static_descs, n_static = source.descs, source.n_descs
+            packed_ptr, static_bytes, peer_bytes, fused = src_ptr, max(source.span_bytes, 1), source.peer_bytes, True
+        elif fused:
             if src_is_peer:
                 for i in range(n_static):
                     static_descs[i].flags |= _native.SH_DESC_PEER_SOURCE
@@ -224,7 +247,7 @@ class Int8BlockStreamer:
             peer_bytes = image.static_bytes if src_is_peer else 0
         if n_static:
             _native.check(self._lib.sh_dequant_block_async(
-                static_descs, n_static, packed_ptr, image.static_bytes, out_slab.tensor.data_ptr(), image.out_bytes,
+                static_descs, n_static, packed_ptr, static_bytes, out_slab.tensor.data_ptr(), image.out_bytes,
                 image.out_dtype_code, dq, self.status.data_ptr()), f"sh_dequant_block_async({image.block_id})")
             launches += -(-n_static // 32)
         if not fused:

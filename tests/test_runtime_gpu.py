@@ -123,6 +123,41 @@ def test_resident_blocks_are_hits_on_later_steps(tmp_path: Path) -> None:
     rt.shutdown()
 
 
+@pytest.mark.parametrize("layout,fused,world", [("owner", True, 3), ("owner", False, 3), ("striped", True, 3),
+                                               ("striped", True, 8)])
+def test_sharded_layouts_emulated_on_one_gpu(layout: str, fused: bool, world: int, tmp_path: Path) -> None:
+    """One process plays every rank: arenas for all ranks on this GPU, peers read through the plain-load path.
+
+    Bit-exact block images and the forward within tolerance, for the owner layout (fused and copy-engine
+    staged) and for the row-striped layout (absolute-address descriptors).
+    """
+    from stagehand_b200.sharded import DeviceImageStore
+
+    model, rt, x = _build("cfg1", tmp_path)
+    store = DeviceImageStore(rt, layout=layout, fused=fused, emulate_world=world)
+    rt.begin_step(0)
+    with torch.inference_mode(), rt.managed_forward():
+        y = model(x)
+    torch.cuda.synchronize()
+    assert rt._scheduler._streamer.read_status() == 0
+    digests = []
+    for entry in rt._registry.blocks_in_order():
+        img = rt._residency.get_entry(entry.block_id).gpu_tensor.view(torch.uint8).cpu().numpy()
+        digests.append(hashlib.sha256(img.tobytes()).hexdigest())
+    assert digests == [str(d) for d in G["cfg1__block_sha256"]]
+    assert _rel_l2(y, "cfg1") <= 1e-2
+    m = rt._telemetry._current
+    total_int8 = sum(rt._scheduler._image_plan(e).static_bytes for e in rt._registry.blocks_in_order())
+    if layout == "owner":
+        assert 0.4 * total_int8 < m.peer_bytes < total_int8          # blocks 1 and 2 of 4 are "remote" at world 3
+    else:
+        assert abs(m.peer_bytes - total_int8 * (world - 1) / world) < 0.05 * total_int8
+    assert m.link_bytes < 4 * 20_000
+    rt.end_step()
+    rt.shutdown()
+    store.close()
+
+
 def test_device_resident_images_fused_and_staged(tmp_path: Path) -> None:
     """INT8 images parked in HBM (the single-GPU form of the sharded layout): same bits, no host-link bytes."""
     from stagehand_b200.sharded import park_images_in_hbm

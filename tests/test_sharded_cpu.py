@@ -77,3 +77,75 @@ def test_two_ranks_rebuild_every_block_from_the_owner(tmp_path) -> None:
     world = 2
     mp.spawn(_rank_main, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     assert all((tmp_path / f"ok{r}").exists() for r in range(world))
+
+
+def test_stripes_cover_every_row_once_and_rebuild_the_block() -> None:
+    """Striped layout: arenas built from the full image + the consumer's stripe descriptors expand to the same slab."""
+    from desc_interp import expand
+    from stagehand_b200 import _native
+    from stagehand_b200._native import ShParamDesc
+    from stagehand_b200.sharded import plan_block_stripes, stripe_bounds
+
+    assert stripe_bounds(10, 4) == [0, 0, 4, 4, 10] and stripe_bounds(4096, 8)[3] == 1536
+    rng = np.random.default_rng(4)
+    # a hand-made block image: two weights (one with zero points), a bias to cast, raw bytes to copy, a zero row
+    image = np.zeros(1 << 16, dtype=np.uint8)
+    descs, cursor, dst = [], 0, 0
+
+    def put(data: np.ndarray, align: int) -> int:
+        nonlocal cursor
+        cursor = -(-cursor // align) * align
+        raw = np.ascontiguousarray(data).view(np.uint8).reshape(-1)
+        image[cursor : cursor + raw.size] = raw
+        at = cursor
+        cursor += -(-raw.size // 16) * 16 + 16
+        return at
+
+    for rows, cols, with_zp in ((37, 48, False), (64, 32, True), (3, 16, False)):
+        q = put(rng.integers(-128, 128, size=(rows, cols), dtype=np.int8), 256)
+        s = put(np.exp(rng.standard_normal(rows)).astype(np.float32), 16)
+        z = put(rng.standard_normal(rows).astype(np.float32), 16) if with_zp else -1
+        descs.append(ShParamDesc(kind=_native.SH_KIND_DEQUANT_I8, flags=0, src_off=q, scale_off=s, zp_off=z, dst_off=dst,
+                                 rows=rows, cols=cols, ld=cols))
+        dst += rows * cols * 2
+    b = put(rng.standard_normal(40).astype(np.float32), 16)
+    descs.append(ShParamDesc(kind=_native.SH_KIND_CAST_F32, flags=0, src_off=b, scale_off=0, zp_off=-1, dst_off=dst,
+                             rows=1, cols=40, ld=0))
+    dst += 80
+    c = put(rng.integers(0, 256, size=24, dtype=np.uint8), 16)
+    descs.append(ShParamDesc(kind=_native.SH_KIND_COPY, flags=0, src_off=c, scale_off=0, zp_off=-1, dst_off=dst,
+                             rows=1, cols=24, ld=0))
+    dst += 24
+    descs.append(ShParamDesc(kind=_native.SH_KIND_ZERO, flags=0, src_off=0, scale_off=0, zp_off=-1, dst_off=dst,
+                             rows=1, cols=8, ld=0))
+    dst += 8
+    expected = expand(image, descs, len(descs), dst, _native.SH_DT_BF16)
+
+    for world in (1, 2, 3, 8):
+        arena_cursor = [0] * world
+        arena_cursor[0] = 100                                   # a previous block left the cursor unaligned
+        stripes = plan_block_stripes(descs, 2, world, home_rank=world - 1, arena_cursor=arena_cursor)
+        arenas = [np.zeros(arena_cursor[r] + 64, dtype=np.uint8) for r in range(world)]
+        spans: list[list[tuple[int, int]]] = [[] for _ in range(world)]
+        for p in stripes.pieces:
+            arenas[p.rank][p.arena_off : p.arena_off + p.nbytes] = image[p.full_off : p.full_off + p.nbytes]
+            spans[p.rank].append((p.arena_off, p.arena_off + p.nbytes))
+        for r in range(world):                                  # pieces never overlap inside an arena
+            ordered = sorted(spans[r])
+            assert all(a[1] <= b[0] for a, b in zip(ordered, ordered[1:]))
+        out = np.full(dst, 0xEE, dtype=np.uint8)
+        covered = np.zeros(dst, dtype=np.int32)
+        for d in stripes.descs:                                 # expand each stripe against its own rank's arena
+            one = ShParamDesc(kind=d.kind, flags=0, src_off=d.src_off, scale_off=d.scale_off, zp_off=d.zp_off,
+                              dst_off=d.dst_off, rows=d.rows, cols=d.cols, ld=d.ld)
+            part = expand(arenas[d.rank], [one], 1, dst, _native.SH_DT_BF16)
+            touched = part != 0xEE
+            nbytes = d.rows * d.cols * 2 if d.kind in (_native.SH_KIND_DEQUANT_I8, _native.SH_KIND_CAST_F32) else d.cols
+            covered[d.dst_off : d.dst_off + nbytes] += 1
+            out[d.dst_off : d.dst_off + nbytes] = part[d.dst_off : d.dst_off + nbytes]
+            assert d.src_off % 16 == 0 and d.scale_off % 16 == 0
+        assert np.all(covered == 1)                             # every output byte produced exactly once
+        assert np.array_equal(out, expected)
+        if world == 8:                                          # the load is spread: no rank holds most of the bytes
+            per_rank = [sum(p.nbytes for p in stripes.pieces if p.rank == r) for r in range(world)]
+            assert max(per_rank) < 0.4 * sum(per_rank)

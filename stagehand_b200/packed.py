@@ -72,6 +72,7 @@ class _DynamicRow:
     slot_bytes: int
     numel: int
     dst_off: int
+    staged_from: Any = None       # (data_ptr, version, dtype, base) of the tensor last written into the slot
 
 
 @dataclass
@@ -114,12 +115,15 @@ class PackedBlockImage:
                 buffer[op.offset : op.offset + op.nbytes].view(t.dtype).copy_(t.reshape(-1))
 
     def refresh_dynamic(self, buffer: torch.Tensor, module: nn.Module | None,
-                        cache: MutableMapping[str, torch.Tensor] | None, base_offset: int = 0) -> None:
+                        cache: MutableMapping[str, torch.Tensor] | None, base_offset: int = 0,
+                        persistent: bool = False) -> None:
         """Stage the live module-owned parameters (reference ``scheduler.py:310-325``).
 
         A parameter whose element count matches is read from the module (and
         remembered in *cache* the first time); one emptied by eviction comes from
-        *cache*; anything else becomes a zero-fill descriptor.
+        *cache*; anything else becomes a zero-fill descriptor.  With *persistent* (the buffer is this
+        block's own long-lived image, never lent to another block) a slot whose source tensor is the
+        same object and has not been modified since it was staged is left as it is.
         """
         if not self.dynamic_rows:
             return
@@ -135,9 +139,14 @@ class PackedBlockImage:
             elif cache is not None and row.name in cache:
                 source = cache[row.name]
             if source is None or source.device.type == "meta":
+                row.staged_from = None
                 desc.kind = SH_KIND_ZERO
                 desc.cols = row.numel * self.runtime_dtype.itemsize
                 continue
+            stamp = (buffer.data_ptr(), source.data_ptr(), source._version, source.dtype, base_offset)
+            if persistent and row.staged_from == stamp and desc.kind != SH_KIND_ZERO:
+                continue          # same tensor, not modified since it was last staged: the slot is current
+            row.staged_from = stamp
             flat = source.detach().reshape(-1)
             if flat.device.type != "cpu":
                 flat = flat.cpu()

@@ -197,6 +197,7 @@ class StagehandScheduler:
         self._device_source_fused = True
         self._deferred_slabs: list[tuple[Any, "PinnedSlab"]] = []   # (copied event, pool slab) awaiting DMA completion
         self._squareq_v2_loader: Any = None
+        self._empties: dict[torch.dtype, torch.Tensor] = {}
 
     # ── step lifecycle ───────────────────────────────────────────────
 
@@ -537,7 +538,7 @@ class StagehandScheduler:
         if plan.dynamic_rows:
             if image.last_copy is not None and not image.last_copy.done():
                 image.last_copy.wait(60_000)   # the previous DMA of this image still reads the dynamic section
-            plan.refresh_dynamic(image.buffer, module, cache)
+            plan.refresh_dynamic(image.buffer, module, cache, persistent=slab is None)
         return image, slab
 
     def _load_squareq_block(self, block_id: str, entry: "BlockEntry", res: "ResidencyEntry", state: BlockState) -> None:
@@ -578,7 +579,7 @@ class StagehandScheduler:
         if image.last_copy is not None and not image.last_copy.done():
             image.last_copy.wait(60_000)
         plan.refresh_dynamic(image.buffer, entry.module_ref(), self._module_param_caches.setdefault(entry.block_id, {}),
-                             base_offset=plan.static_bytes)
+                             base_offset=plan.static_bytes, persistent=True)
         return image, None
 
     def set_device_sources(self, sources: dict[str, Any], fused: bool = True) -> None:
@@ -770,16 +771,25 @@ class StagehandScheduler:
             if source_backed:
                 mutable = set(entry.module_param_names)
                 keep_on_gpu = self._defer_backward_eviction and not self._backward_phase
+                frozen_cache = self._module_param_caches.get(block_id) if self._inference_mode else None
                 for name, _shape, dtype, _off, _numel in res.param_layout:
                     if name in mutable:
                         live = _get_param_data(module, name)
+                        cached = frozen_cache.get(name) if frozen_cache else None
+                        if (cached is not None and not keep_on_gpu and cached.dtype == live.dtype
+                                and cached.numel() == live.numel() and not getattr(live, "requires_grad", False)):
+                            # Inference: the value staged from the host has not changed, so the host copy
+                            # kept since the first staging stands in for a device-to-host read (which
+                            # would stall the host until the GPU has caught up).
+                            _set_param_data(module, name, cached)
+                            continue
                         target = live.device if keep_on_gpu else torch.device("cpu")
                         _set_param_data(module, name, live.to(target).clone())
                     elif (entry.file_param_specs and self._backward_phase and self._defer_backward_eviction
                           and self._restore_cpu_file_view(entry, module, name, dtype)):
                         pass
                     else:
-                        _set_param_data(module, name, torch.empty(0, dtype=dtype))
+                        _set_param_data(module, name, self._empty(dtype))
                 if save_back:
                     for name, param in module.named_parameters():
                         if name in mutable and param.grad is not None and param.grad.device.type != "cpu":
@@ -793,6 +803,13 @@ class StagehandScheduler:
                             param.grad = param.grad.to("cpu")
         self._release_device_storage(res)
         self._residency.transition(block_id, BlockState.UNLOADED)
+
+    def _empty(self, dtype: torch.dtype) -> torch.Tensor:
+        """The zero-element tensor evicted frozen parameters point at (one per dtype, shared)."""
+        hit = self._empties.get(dtype)
+        if hit is None:
+            hit = self._empties[dtype] = torch.empty(0, dtype=dtype)
+        return hit
 
     def _restore_cpu_file_view(self, entry: "BlockEntry", module: nn.Module, name: str, dtype: torch.dtype) -> bool:
         """During deferred backward eviction a frozen file-backed parameter becomes a CPU view of its file region."""

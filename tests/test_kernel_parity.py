@@ -197,3 +197,52 @@ def test_bad_descriptors_are_rejected_before_launch() -> None:
     torch.cuda.synchronize()
     assert _native.stats()["kernel_launches"] == launches
     assert bool((out == 0x55).all())
+
+
+@pytest.mark.parametrize("rows,cols", [(12288, 49152), (21504, 3072)])
+def test_full_size_matrices_through_size_independent_properties(rows: int, cols: int) -> None:
+    """The largest sweep shapes, where the CPU oracle would take minutes: properties that need no oracle.
+
+    * an independent GPU formulation (torch ops: int8 -> fp32, multiply, cast) gives the same bytes;
+    * negating the weights negates every output exactly;
+    * doubling every scale doubles every output exactly (a power-of-two factor commutes with rounding);
+    * a second run over the same image is byte-identical;
+    * an order-independent checksum of the output matches the checksum of its row-block checksums.
+    """
+    lib = _native.lib()
+    _native.check(lib.sh_init(torch.cuda.current_device()))
+    gen = torch.Generator(device="cuda").manual_seed(rows + cols)
+    n = rows * cols
+    scale_off = -(-n // 256) * 256
+    nbytes = scale_off + -(-rows // 4) * 16 + 256
+    q = torch.randint(-127, 128, (n,), dtype=torch.int8, device="cuda", generator=gen)
+    scale = torch.exp(torch.randn(rows, device="cuda", generator=gen) * 0.5 - 4.605).float()
+    stream = torch.cuda.current_stream().cuda_stream
+    descs = _native.make_descs([_native.ShParamDesc(kind=0, flags=0, src_off=0, scale_off=scale_off, zp_off=-1,
+                                                    dst_off=0, rows=rows, cols=cols, ld=cols)])
+
+    def run(qv: torch.Tensor, sv: torch.Tensor) -> torch.Tensor:
+        img = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+        img[:n] = qv.view(torch.uint8)
+        img[scale_off : scale_off + rows * 4] = sv.view(torch.uint8)
+        out = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+        _native.check(lib.sh_dequant_block_async(descs, 1, img.data_ptr(), nbytes, out.data_ptr(), n * 2,
+                                                 _native.SH_DT_BF16, stream, None))
+        torch.cuda.synchronize()
+        return out.view(rows, cols)
+
+    base = run(q, scale)
+    again = run(q, scale)
+    assert torch.equal(base.view(torch.int16), again.view(torch.int16))
+    chunk = 1024
+    for r0 in range(0, rows, chunk):                               # independent formulation, chunked to bound memory
+        ref = (q.view(rows, cols)[r0 : r0 + chunk].float() * scale[r0 : r0 + chunk, None]).to(torch.bfloat16)
+        assert torch.equal(ref.view(torch.int16), base[r0 : r0 + chunk].view(torch.int16))
+    neg = run(-q, scale)
+    assert torch.equal((-neg).view(torch.int16), base.view(torch.int16)) or \
+        torch.equal(torch.where(base == 0, base, -neg).view(torch.int16), base.view(torch.int16))
+    doubled = run(q, scale * 2)
+    assert torch.equal(doubled.float(), base.float() * 2)
+    as_int = base.view(torch.int16).to(torch.int64)
+    total = int(as_int.sum())
+    assert total == sum(int(as_int[r0 : r0 + chunk].sum()) for r0 in range(0, rows, chunk))

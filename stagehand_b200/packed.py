@@ -90,6 +90,7 @@ class PackedBlockImage:
     static_ops: list[_StaticOp] = field(default_factory=list)
     dynamic_rows: list[_DynamicRow] = field(default_factory=list)
     _static_split: Any = None
+    last_source: dict[str, int] = field(default_factory=dict)   # dynamic row -> data_ptr of the tensor last staged
 
     @property
     def out_dtype_code(self) -> int:
@@ -140,11 +141,15 @@ class PackedBlockImage:
                 source = cache[row.name]
             if source is None or source.device.type == "meta":
                 row.staged_from = None
+                self.last_source.pop(row.name, None)
                 desc.kind = SH_KIND_ZERO
                 desc.cols = row.numel * self.runtime_dtype.itemsize
                 continue
-            stamp = (buffer.data_ptr(), source.data_ptr(), source._version, source.dtype, base_offset)
-            if persistent and row.staged_from == stamp and desc.kind != SH_KIND_ZERO:
+            self.last_source[row.name] = source.data_ptr()
+            # inference tensors carry no version counter: they are always restaged
+            stamp = None if source.is_inference() else (
+                buffer.data_ptr(), source.data_ptr(), source._version, source.dtype, base_offset)
+            if persistent and stamp is not None and row.staged_from == stamp and desc.kind != SH_KIND_ZERO:
                 continue          # same tensor, not modified since it was last staged: the slot is current
             row.staged_from = stamp
             flat = source.detach().reshape(-1)

@@ -198,6 +198,7 @@ class StagehandScheduler:
         self._deferred_slabs: list[tuple[Any, "PinnedSlab"]] = []   # (copied event, pool slab) awaiting DMA completion
         self._squareq_v2_loader: Any = None
         self._empties: dict[torch.dtype, torch.Tensor] = {}
+        self._evicted_copies: dict[str, dict[str, torch.Tensor]] = {}   # block -> name -> CPU copy in the runtime dtype
 
     # ── step lifecycle ───────────────────────────────────────────────
 
@@ -337,6 +338,7 @@ class StagehandScheduler:
         self._file_maps.clear()
         self._squareq_layers.clear()
         self._module_param_caches.clear()
+        self._evicted_copies.clear()
 
     # ── per-block hooks ──────────────────────────────────────────────
 
@@ -771,20 +773,26 @@ class StagehandScheduler:
             if source_backed:
                 mutable = set(entry.module_param_names)
                 keep_on_gpu = self._defer_backward_eviction and not self._backward_phase
-                frozen_cache = self._module_param_caches.get(block_id) if self._inference_mode else None
+                # Inference: a module-owned parameter's value does not change while it sits in VRAM, so the
+                # host copy made at its first eviction stands in for every later device-to-host read
+                # (each of which would stall the host until the GPU has caught up).
+                host_copies = self._evicted_copies.setdefault(block_id, {}) if self._inference_mode else None
+                image_plan = self._image_plans.get(block_id)
+                staged_ptrs = image_plan.last_source if image_plan is not None else {}
                 for name, _shape, dtype, _off, _numel in res.param_layout:
                     if name in mutable:
                         live = _get_param_data(module, name)
-                        cached = frozen_cache.get(name) if frozen_cache else None
-                        if (cached is not None and not keep_on_gpu and cached.dtype == live.dtype
-                                and cached.numel() == live.numel() and not getattr(live, "requires_grad", False)):
-                            # Inference: the value staged from the host has not changed, so the host copy
-                            # kept since the first staging stands in for a device-to-host read (which
-                            # would stall the host until the GPU has caught up).
-                            _set_param_data(module, name, cached)
+                        kept = host_copies.get(name) if host_copies is not None else None
+                        if (kept is not None and not keep_on_gpu and kept.dtype == live.dtype
+                                and kept.shape == live.shape and staged_ptrs.get(name) == kept.data_ptr()):
+                            _set_param_data(module, name, kept)
                             continue
                         target = live.device if keep_on_gpu else torch.device("cpu")
-                        _set_param_data(module, name, live.to(target).clone())
+                        with torch.inference_mode(False):
+                            moved = live.to(target).clone()
+                        _set_param_data(module, name, moved)
+                        if host_copies is not None and not keep_on_gpu:
+                            host_copies[name] = moved
                     elif (entry.file_param_specs and self._backward_phase and self._defer_backward_eviction
                           and self._restore_cpu_file_view(entry, module, name, dtype)):
                         pass

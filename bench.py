@@ -38,6 +38,11 @@ ROOT = Path(__file__).resolve().parent
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
+# ncu (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic bytes for the block kernel: 151.1 MB read
+# (1.00 B per weight) + 243.9 MB written of the 302 MB produced -- the rest is still dirty in the 126 MB L2 when
+# the kernel ends -- over 453 MB algorithmic.
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 0.872
+
 METRIC = "delivered_bf16_weight_GBps"
 UNIT = "GB/s"
 
@@ -417,6 +422,8 @@ def main() -> None:
             run_kernel_sweep(args)
         return
 
+    if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+        os.environ["NCCL_DEBUG"] = "WARN"        # keep stdout to the one JSON line
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -517,7 +524,11 @@ def compose_line(args, world: int, results: dict, peaks: dict, link_peak: float,
             return None
         achieved = 3.0 * prof["elements"] / (prof["kernel_ms"] / 1e3) / 1e9
         return {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                "frac": achieved / peaks["hbm_gbs"],
+                "traffic": NCU_TRAFFIC_PER_ALGORITHMIC_BYTE * 3.0 * prof["elements"] / prof["launches"],
+                "traffic_source": "dram bytes read+written per launch, scaled by weights processed from the ncu capture "
+                                  "of a 151 M-weight launch (profiles/sq_block_kernel_12288x12288_ncu_full.md)",
+                "peak_source": peaks["source"],
                 "launches": prof["launches"], "mean_launch_ms": prof["kernel_ms"] / prof["launches"],
                 "algorithmic_bytes_per_launch": 3.0 * prof["elements"] / prof["launches"]}
 

@@ -279,7 +279,9 @@ class DeviceImageStore:
             return sources
         for block_id, bs in self.stripes.items():
             rows = []
-            for d in bs.descs:
+            # Each consumer walks the owners in its own rotation (rank+1, rank+2, ..., itself last), so that
+            # ranks running in step read from different GPUs at any moment instead of all queueing on one.
+            for d in sorted(bs.descs, key=lambda d: (d.rank - self.rank - 1) % self.world):
                 base = self._arenas.get(d.rank, 0)
                 flags = 0 if d.kind == SH_KIND_ZERO else SH_DESC_ABSOLUTE | (SH_DESC_PEER_SOURCE if d.rank != self.rank else 0)
                 rows.append(ShParamDesc(

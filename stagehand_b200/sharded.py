@@ -98,6 +98,7 @@ class StripeDesc:
     rows: int
     cols: int
     ld: int
+    weight: int = 0      # index of the block descriptor this stripe was cut from
 
 
 @dataclass
@@ -130,7 +131,8 @@ def plan_block_stripes(static_descs: Sequence[Any], itemsize: int, world: int, h
         arena_cursor[rank] = at + int(reserve if reserve is not None else nbytes)
         return at
 
-    for d in static_descs:
+    for weight, d in enumerate(static_descs):
+        n_before = len(out.descs)
         if d.kind == SH_KIND_DEQUANT_I8:
             rows, cols, ld = int(d.rows), int(d.cols), int(d.ld)
             bounds = stripe_bounds(rows, world)
@@ -150,6 +152,8 @@ def plan_block_stripes(static_descs: Sequence[Any], itemsize: int, world: int, h
             nbytes = int(d.cols) * (4 if d.kind == _native.SH_KIND_CAST_F32 else 1)
             src = place(home_rank, d.src_off, nbytes, 16, reserve=_up(nbytes, 16))
             out.descs.append(StripeDesc(int(d.kind), home_rank, src, 0, -1, int(d.dst_off), 1, int(d.cols), 0))
+        for made in out.descs[n_before:]:
+            made.weight = weight
     return out
 
 
@@ -279,9 +283,15 @@ class DeviceImageStore:
             return sources
         for block_id, bs in self.stripes.items():
             rows = []
-            # Each consumer walks the owners in its own rotation (rank+1, rank+2, ..., itself last), so that
-            # ranks running in step read from different GPUs at any moment instead of all queueing on one.
-            for d in sorted(bs.descs, key=lambda d: (d.rank - self.rank - 1) % self.world):
+            # Stripes stay grouped by weight (so a launch reads from several owners at once), but inside each
+            # weight every consumer starts with a different owner (rank+1, rank+2, ..., itself last): ranks
+            # running in step then do not all queue on the same GPU's egress.
+            groups: dict[int, list[Any]] = {}
+            for d in bs.descs:
+                groups.setdefault(d.weight, []).append(d)
+            rotated = [d for _w, ds in sorted(groups.items())
+                       for d in sorted(ds, key=lambda d: (d.rank - self.rank - 1) % self.world)]
+            for d in rotated:
                 base = self._arenas.get(d.rank, 0)
                 flags = 0 if d.kind == SH_KIND_ZERO else SH_DESC_ABSOLUTE | (SH_DESC_PEER_SOURCE if d.rank != self.rank else 0)
                 rows.append(ShParamDesc(

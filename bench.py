@@ -409,6 +409,11 @@ def kernel_profile(native, timeout_ms: int = 120_000) -> dict:
 
 def main() -> None:
     args = parse_args()
+    # Libraries (NCCL's banner, torchrun notices) may write to stdout; the contract is ONE JSON line there.
+    # Everything else goes to stderr, the line is written to the real stdout at the end.
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+    sys.stdout = os.fdopen(real_stdout, "w", buffering=1)
     if args.impl == "reference":
         run_reference_arm(args)
         return

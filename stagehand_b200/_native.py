@@ -26,6 +26,7 @@ SH_DT_BF16, SH_DT_F16, SH_DT_F32 = 0, 1, 2
 SH_DESC_PEER_SOURCE = 1
 SH_DESC_ABSOLUTE = 2
 SH_NOALLOC_MAX_BYTES = 32 * 1024 * 1024
+MAX_DESCS_PER_LAUNCH = 128     # sq::kMaxDescs
 
 
 class ShParamDesc(ctypes.Structure):

@@ -20,7 +20,7 @@ namespace {
 static __device__ __align__(256) unsigned char g_noalloc_staging[SH_NOALLOC_MAX_BYTES];
 
 constexpr int kMaxDevices = 64;
-constexpr int kMaxPlans = 4;                 // up to kMaxPlans * 32 descriptors per call, all on the stack
+constexpr int kMaxPlans = 1;                 // one launch plan (128 descriptors) per call, on the stack
 std::mutex g_setup_mu;
 void* g_staging_ptr[kMaxDevices] = {nullptr};
 

@@ -379,8 +379,12 @@ __global__ void __launch_bounds__(kThreads, SQ_MIN_CTAS_PER_SM) sq_block_kernel(
     __shared__ alignas(8) uint64_t s_bar;
 
     const uint32_t tile = blockIdx.x;
+    // descriptor of this tile: the last d with tile_begin[d] <= tile (binary search, uniform across the CTA)
     int d = 0;
-    while (d + 1 < plan.n_desc && tile >= plan.tile_begin[d + 1]) ++d;
+    for (int hi = plan.n_desc; hi - d > 1;) {
+        const int mid = (d + hi) >> 1;
+        if (tile >= plan.tile_begin[mid]) d = mid; else hi = mid;
+    }
     const DescDev& D = plan.d[d];
     const int64_t local_tile = static_cast<int64_t>(tile - plan.tile_begin[d]);
 

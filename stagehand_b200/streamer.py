@@ -203,7 +203,7 @@ class Int8BlockStreamer:
         staging.last_use = acquire_event().record(self.dequant_stream)
         release_event(host.last_copy)
         host.last_copy = acquire_event().record(self.copy_stream)   # the ticket owns `copied`; the image its own
-        launches = -(-image.n_descs // 32)
+        launches = -(-image.n_descs // _native.MAX_DESCS_PER_LAUNCH)
         return StreamTicket(image.block_id, ready, copied, link_bytes=image.total_bytes, launches=launches)
 
     def submit_from_device(self, image: PackedBlockImage, source: DeviceSource, fused: bool,
@@ -249,7 +249,7 @@ class Int8BlockStreamer:
             _native.check(self._lib.sh_dequant_block_async(
                 static_descs, n_static, packed_ptr, static_bytes, out_slab.tensor.data_ptr(), image.out_bytes,
                 image.out_dtype_code, dq, self.status.data_ptr()), f"sh_dequant_block_async({image.block_id})")
-            launches += -(-n_static // 32)
+            launches += -(-n_static // _native.MAX_DESCS_PER_LAUNCH)
         if not fused:
             release_event(staging.last_use)
             staging.last_use = acquire_event().record(self.dequant_stream)
@@ -273,7 +273,7 @@ class Int8BlockStreamer:
             release_event(dynamic_host.last_copy)
             dynamic_host.last_copy = dyn_copied
             link_bytes = dyn_bytes
-            launches += -(-n_dyn // 32)
+            launches += -(-n_dyn // _native.MAX_DESCS_PER_LAUNCH)
         ready = acquire_event().record(self.dequant_stream)
         return StreamTicket(image.block_id, ready, copied, link_bytes=link_bytes, peer_bytes=peer_bytes,
                             launches=launches)

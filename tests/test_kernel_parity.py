@@ -129,7 +129,7 @@ def test_more_descriptors_than_one_launch_holds() -> None:
     rng = np.random.default_rng(21)
     img = HandImage()
     expect = []
-    for i in range(75):
+    for i in range(300):
         rows, cols = 3 + i % 5, 16 * (1 + i % 4)
         q = rng.integers(-128, 128, size=(rows, cols), dtype=np.int8)
         scale = np.exp(rng.standard_normal(rows)).astype(np.float32)

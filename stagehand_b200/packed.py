@@ -117,17 +117,19 @@ class PackedBlockImage:
 
     def refresh_dynamic(self, buffer: torch.Tensor, module: nn.Module | None,
                         cache: MutableMapping[str, torch.Tensor] | None, base_offset: int = 0,
-                        persistent: bool = False) -> None:
+                        persistent: bool = False) -> bool:
         """Stage the live module-owned parameters (reference ``scheduler.py:310-325``).
 
         A parameter whose element count matches is read from the module (and
         remembered in *cache* the first time); one emptied by eviction comes from
         *cache*; anything else becomes a zero-fill descriptor.  With *persistent* (the buffer is this
         block's own long-lived image, never lent to another block) a slot whose source tensor is the
-        same object and has not been modified since it was staged is left as it is.
+        same object and has not been modified since it was staged is left as it is.  Returns whether
+        anything in the dynamic section (bytes or descriptor kinds) changed.
         """
         if not self.dynamic_rows:
-            return
+            return False
+        changed = False
         live = dict(module.named_parameters()) if module is not None else {}
         for row in self.dynamic_rows:
             desc = self.descs[row.desc_index]
@@ -140,6 +142,7 @@ class PackedBlockImage:
             elif cache is not None and row.name in cache:
                 source = cache[row.name]
             if source is None or source.device.type == "meta":
+                changed = changed or desc.kind != SH_KIND_ZERO or row.staged_from is not None
                 row.staged_from = None
                 self.last_source.pop(row.name, None)
                 desc.kind = SH_KIND_ZERO
@@ -151,6 +154,7 @@ class PackedBlockImage:
                 buffer.data_ptr(), source.data_ptr(), source._version, source.dtype, base_offset)
             if persistent and stamp is not None and row.staged_from == stamp and desc.kind != SH_KIND_ZERO:
                 continue          # same tensor, not modified since it was last staged: the slot is current
+            changed = True
             row.staged_from = stamp
             flat = source.detach().reshape(-1)
             if flat.device.type != "cpu":
@@ -171,6 +175,7 @@ class PackedBlockImage:
             nbytes = flat.numel() * flat.element_size()
             at = row.offset - base_offset   # base_offset = static_bytes when *buffer* holds the dynamic section only
             buffer[at : at + nbytes].view(flat.dtype).copy_(flat)
+        return changed
 
     # ── descriptor views ─────────────────────────────────────────────
 

@@ -580,8 +580,9 @@ class StagehandScheduler:
             raise StagehandOOMError(f"no pinned memory left for the dynamic section of block {entry.block_id!r}")
         if image.last_copy is not None and not image.last_copy.done():
             image.last_copy.wait(60_000)
-        plan.refresh_dynamic(image.buffer, entry.module_ref(), self._module_param_caches.setdefault(entry.block_id, {}),
-                             base_offset=plan.static_bytes, persistent=True)
+        if plan.refresh_dynamic(image.buffer, entry.module_ref(), self._module_param_caches.setdefault(entry.block_id, {}),
+                                base_offset=plan.static_bytes, persistent=True):
+            image.dirty = True
         return image, None
 
     def set_device_sources(self, sources: dict[str, Any], fused: bool = True) -> None:

@@ -39,6 +39,7 @@ class HostImage:
     nbytes: int
     pinned: bool
     static_ready: bool = False    # static section already written
+    dirty: bool = True            # dynamic section rewritten since it was last copied to the device
     last_copy: Event | None = None
     _raw_ptr: int = 0             # sh_host_alloc pointer to free (0 when torch owns the memory)
 
@@ -152,6 +153,8 @@ class Int8BlockStreamer:
         self._dyn_ring: StagingRing | None = None
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self._lib = lib
+        # device-resident copies of blocks' dynamic sections: block_id -> [tensor, merged descs, n, last_read event]
+        self._dyn_resident: dict[str, list] = {}
 
     # ── staging ──────────────────────────────────────────────────────
 
@@ -245,6 +248,9 @@ class Int8BlockStreamer:
             copied.block_stream(self.dequant_stream)
             packed_ptr = staging.tensor.data_ptr()
             peer_bytes = image.static_bytes if src_is_peer else 0
+        if fused and n_dyn:
+            return self._submit_merged(image, source, static_descs, n_static, dyn_descs, n_dyn, packed_ptr, static_bytes,
+                                       peer_bytes, dynamic_host, out_slab)
         if n_static:
             _native.check(self._lib.sh_dequant_block_async(
                 static_descs, n_static, packed_ptr, static_bytes, out_slab.tensor.data_ptr(), image.out_bytes,
@@ -277,6 +283,56 @@ class Int8BlockStreamer:
         ready = acquire_event().record(self.dequant_stream)
         return StreamTicket(image.block_id, ready, copied, link_bytes=link_bytes, peer_bytes=peer_bytes,
                             launches=launches)
+
+    def _submit_merged(self, image: PackedBlockImage, source: DeviceSource, static_descs: Any, n_static: int,
+                       dyn_descs: Any, n_dyn: int, packed_ptr: int, static_bytes: int, peer_bytes: int,
+                       dynamic_host: HostImage | None, out_slab: DeviceSlab) -> StreamTicket:
+        """Fused path with module-owned parameters: ONE launch for the whole block.
+
+        The block's dynamic section is kept resident in a small device buffer and re-copied only when
+        the host staged something new; its descriptors carry that buffer's absolute address and ride in
+        the same launch as the static ones.
+        """
+        if dynamic_host is None:
+            raise TransferError(f"block {image.block_id!r} has module-owned parameters but no dynamic image")
+        dyn_bytes = image.total_bytes - image.static_bytes
+        entry = self._dyn_resident.get(image.block_id)
+        link_bytes = 0
+        if entry is None or dynamic_host.dirty or entry[0].numel() < dyn_bytes:
+            if entry is None or entry[0].numel() < dyn_bytes:
+                entry = [torch.empty(dyn_bytes, dtype=torch.uint8, device=self.device), None, 0, None]
+                self._dyn_resident[image.block_id] = entry
+                fresh = acquire_event().record(torch.cuda.current_stream(self.device))
+                fresh.block_stream(self.copy_stream)     # memory handed out by the allocator may still be in use there
+                release_event(fresh)
+            if entry[3] is not None:
+                entry[3].block_stream(self.copy_stream)          # the last kernel that read the buffer is done
+            _native.check(self._lib.sh_copy_h2d_async(entry[0].data_ptr(), dynamic_host.buffer.data_ptr(), dyn_bytes,
+                                                      stream_handle(self.copy_stream)), "sh_copy_h2d_async")
+            release_event(dynamic_host.last_copy)
+            dynamic_host.last_copy = acquire_event().record(self.copy_stream)
+            dynamic_host.last_copy.block_stream(self.dequant_stream)
+            dynamic_host.dirty = False
+            link_bytes = dyn_bytes
+            merged = [static_descs[i] for i in range(n_static)]
+            base = entry[0].data_ptr()
+            for i in range(n_dyn):
+                d = _native.ShParamDesc()
+                ctypes.memmove(ctypes.byref(d), ctypes.byref(dyn_descs[i]), ctypes.sizeof(_native.ShParamDesc))
+                if d.kind != _native.SH_KIND_ZERO:
+                    d.flags |= _native.SH_DESC_ABSOLUTE
+                    d.src_off += base
+                merged.append(d)
+            entry[1], entry[2] = _native.make_descs(merged), len(merged)
+        _native.check(self._lib.sh_dequant_block_async(
+            entry[1], entry[2], packed_ptr, static_bytes, out_slab.tensor.data_ptr(), image.out_bytes,
+            image.out_dtype_code, stream_handle(self.dequant_stream), self.status.data_ptr()),
+            f"sh_dequant_block_async({image.block_id})")
+        release_event(entry[3])
+        entry[3] = acquire_event().record(self.dequant_stream)
+        ready = acquire_event().record(self.dequant_stream)
+        return StreamTicket(image.block_id, ready, None, link_bytes=link_bytes, peer_bytes=peer_bytes,
+                            launches=-(-entry[2] // _native.MAX_DESCS_PER_LAUNCH))
 
     # ── status ───────────────────────────────────────────────────────
 

@@ -90,7 +90,7 @@ class BlockEntry:
 
     @property
     def squareq_backed(self) -> bool:
-        return self.source_format in ("squareq_bp8", "squareq_v2") and bool(self.squareq_param_specs)
+        return self.source_format in ("squareq_bp8", "squareq_v2", "squareq_packed") and bool(self.squareq_param_specs)
 
     @property
     def eriquant_backed(self) -> bool:
@@ -431,6 +431,8 @@ class BlockRegistry:
             raise FileNotFoundError(f"file-backed source not found: {path}")
         if path.suffix.lower() in (".fpk", ".slab"):
             return self.convert_to_squareq_backed(path, drop_module_tensors=drop_module_tensors)
+        if path.suffix.lower() == ".sqpk":
+            return self.convert_to_packed_backed(path, drop_module_tensors=drop_module_tensors)
         return self._convert_from_index(self._parse_safetensors_index(path), str(path), "safetensors",
                                         drop_module_tensors)
 
@@ -467,6 +469,58 @@ class BlockRegistry:
             raise FileNotFoundError(f"SquareQ slab file not found: {path}")
         return self._convert_from_squareq_meta(self._load_squareq_manifest(path), str(path), "squareq_bp8",
                                                drop_module_tensors)
+
+    def convert_to_packed_backed(self, packed_path: str | Path, *, drop_module_tensors: bool = True) -> int:
+        """Back frozen parameters by a packed-image file (``.sqpk``, see :mod:`stagehand_b200.packed_file`).
+
+        The file records, per block, which parameter comes from which SquareQ layer; a block whose
+        parameter names or shapes differ from the recording is left untouched.
+        """
+        self._require_frozen("convert_to_packed_backed")
+        from stagehand_b200.packed_file import PackedFile
+
+        path = Path(packed_path).expanduser()
+        if not path.exists():
+            raise FileNotFoundError(f"packed image file not found: {path}")
+        packed = PackedFile(path)
+        try:
+            recorded = {
+                bid: {row[0]: SquareQParamSpec(*row) for row in meta["specs"]}
+                for bid, meta in packed.blocks.items()
+            }
+            shapes = {bid: {row[0]: (tuple(row[1]), row[3]) for row in meta["layout"]} for bid, meta in packed.blocks.items()}
+        finally:
+            packed.close()
+
+        compatible: dict[str, bool] = {}
+
+        def block_matches(block_id: str) -> bool:
+            """The module's parameters, in order, are exactly the ones the file was written for."""
+            if block_id not in compatible:
+                module = self._entries[block_id].module_ref()
+                have = [(r[0], tuple(r[1]), r[3]) for r in packed.blocks.get(block_id, {}).get("layout", [])]
+                want = [] if module is None else [(n, tuple(int(d) for d in p.shape), int(p.numel()))
+                                                  for n, p in module.named_parameters()]
+                compatible[block_id] = bool(have) and have == want
+            return compatible[block_id]
+
+        def claim(block_id, pname, _param, shape, numel):
+            if not block_matches(block_id):
+                return None
+            spec = recorded.get(block_id, {}).get(pname)
+            if spec is None or shapes[block_id].get(pname) != (tuple(shape), numel):
+                return None
+            return spec
+
+        def finish(entry, layout, specs, kept):
+            want = [(n, tuple(sh), off, k) for n, sh, _dt, off, k in layout]
+            have = [(r[0], tuple(r[1]), r[2], r[3]) for r in packed.blocks[entry.block_id]["layout"]]
+            if want != have or set(kept) != set(packed.blocks[entry.block_id]["module_param_names"]):
+                raise ValueError(f"block {entry.block_id!r}: parameter layout differs from the one recorded in {path}")
+            return replace(entry, source_path=str(path), source_format="squareq_packed", param_layout=layout,
+                           file_param_specs=(), squareq_param_specs=tuple(specs), module_param_names=kept)
+
+        return self._convert(claim, finish, drop_module_tensors)
 
     def convert_to_squareq_v2_backed(self, safetensors_path: str | Path, manifest_path: str | Path, *,
                                      drop_module_tensors: bool = True) -> int:

@@ -23,6 +23,7 @@ import logging
 import mmap
 import os
 import time
+import warnings
 from pathlib import Path
 from collections.abc import Mapping
 from typing import TYPE_CHECKING, Any, Protocol
@@ -198,6 +199,7 @@ class StagehandScheduler:
         self._deferred_slabs: list[tuple[Any, "PinnedSlab"]] = []   # (copied event, pool slab) awaiting DMA completion
         self._squareq_v2_loader: Any = None
         self._empties: dict[torch.dtype, torch.Tensor] = {}
+        self._packed_files: dict[str, Any] = {}
         self._evicted_copies: dict[str, dict[str, torch.Tensor]] = {}   # block -> name -> CPU copy in the runtime dtype
 
     # ── step lifecycle ───────────────────────────────────────────────
@@ -282,7 +284,9 @@ class StagehandScheduler:
         view = self._file_tensor_views.get(key)
         if view is None:
             raw = self._get_file_view(path)[int(spec.file_offset) : int(spec.file_offset) + int(spec.source_nbytes)]
-            view = torch.frombuffer(raw, dtype=spec.source_dtype).reshape(spec.source_shape)
+            with warnings.catch_warnings():
+                warnings.simplefilter("ignore", UserWarning)  # the mapping is read-only and only ever read
+                view = torch.frombuffer(raw, dtype=spec.source_dtype).reshape(spec.source_shape)
             self._file_tensor_views[key] = view
         return view
 
@@ -328,6 +332,9 @@ class StagehandScheduler:
         if self._device_pool is not None:
             self._device_pool.trim()
         self._image_plans.clear()
+        for packed in self._packed_files.values():
+            packed.close()
+        self._packed_files.clear()
         self._file_tensor_views.clear()
         for fh, mm, view in self._file_maps.values():
             for closer in (view.release, mm.close, fh.close):
@@ -498,6 +505,12 @@ class StagehandScheduler:
             from stagehand_b200.packed import plan_block_image
 
             source = str(entry.source_path)
+            if entry.source_format == "squareq_packed":
+                plan = self._packed_file(source).image_plan(entry.block_id)
+                if plan.out_bytes != entry.size_bytes or plan.runtime_dtype != entry.dtype:
+                    raise ValueError(f"block {entry.block_id!r}: packed image was written for another runtime dtype")
+                self._image_plans[entry.block_id] = plan
+                return plan
             layers = (self._get_squareq_v2_layers(source) if entry.source_format == "squareq_v2"
                       else self._get_squareq_layers(source))
             plan = plan_block_image(
@@ -505,6 +518,15 @@ class StagehandScheduler:
                 set(entry.module_param_names), layers, entry.module_ref(), entry.size_bytes)
             self._image_plans[entry.block_id] = plan
         return plan
+
+    def _packed_file(self, path: str) -> Any:
+        key = str(Path(path).expanduser())
+        hit = self._packed_files.get(key)
+        if hit is None:
+            from stagehand_b200.packed_file import PackedFile
+
+            hit = self._packed_files[key] = PackedFile(key)
+        return hit
 
     def _stage_squareq_image(self, entry: "BlockEntry", plan: "PackedBlockImage") -> tuple["HostImage", Any]:
         """Packed image of *entry* in page-locked memory: ``(image, pool slab or None)``.

@@ -163,3 +163,53 @@ def test_squareq_v2_conversion_with_a_pluggable_loader(tmp_path: Path) -> None:
     ref = t.to(torch.bfloat16).view(torch.int16).numpy().view(np.uint8).reshape(-1)
     assert np.array_equal(out[off : off + numel * 2], ref)            # padded columns dropped, values exact
     rt.shutdown()
+
+
+def test_packed_image_file_round_trip(tmp_path: Path) -> None:
+    """``.fpk`` -> export -> ``.sqpk`` -> convert: same registry entries, same images, one copy per block."""
+    from stagehand_b200.packed_file import PackedFile, export_packed_file
+
+    model = _frozen_tiny()
+    fpk = tmp_path / "m.fpk"
+    write_squareq_fpk(model, BLOCK_PATTERNS["tiny"], fpk, seed=3, pad_in_to=48)
+    rt = _runtime(model)
+    assert rt.convert_registry_to_file_backed(str(fpk)) == 16
+    info = export_packed_file(rt, tmp_path / "m.sqpk")
+    assert info["blocks"] == 2
+    want = {}
+    for entry in rt._registry.blocks_in_order():
+        plan = rt._scheduler._image_plan(entry)
+        buf = torch.zeros(plan.total_bytes, dtype=torch.uint8)
+        plan.fill_static(buf)
+        plan.refresh_dynamic(buf, entry.module_ref(), {})
+        want[entry.block_id] = (expand(buf.numpy(), plan.descs, plan.n_descs, entry.size_bytes, plan.out_dtype_code),
+                                entry.squareq_param_specs, entry.module_param_names, entry.param_layout)
+    rt.shutdown()
+
+    fresh = _frozen_tiny()
+    rt2 = _runtime(fresh)
+    assert rt2.convert_registry_to_file_backed(str(tmp_path / "m.sqpk")) == 16
+    for entry in rt2._registry.blocks_in_order():
+        assert entry.squareq_backed and entry.file_backed and entry.source_format == "squareq_packed"
+        image, specs, kept, layout = want[entry.block_id]
+        assert entry.squareq_param_specs == specs and entry.module_param_names == kept and entry.param_layout == layout
+        assert fresh.blocks[0].qkv.weight.numel() == 0
+        plan = rt2._scheduler._image_plan(entry)
+        assert len(plan.static_ops) == 1                                  # one sequential copy out of the file
+        buf = torch.zeros(plan.total_bytes, dtype=torch.uint8)
+        plan.fill_static(buf)
+        plan.refresh_dynamic(buf, entry.module_ref(), {})
+        out = expand(buf.numpy(), plan.descs, plan.n_descs, entry.size_bytes, plan.out_dtype_code)
+        assert np.array_equal(out, image)
+    rt2.shutdown()
+
+    other = TinyBlockModel(n_blocks=2, hidden=64, heads=2, mlp=64)        # a model the file was not written for
+    for p in other.parameters():
+        p.requires_grad_(False)
+    rt3 = _runtime(other)
+    assert rt3.convert_registry_to_file_backed(str(tmp_path / "m.sqpk")) == 0
+    rt3.shutdown()
+    bad = tmp_path / "bad.sqpk"
+    bad.write_bytes(b"NOTSQPK!" + b"\0" * 64)
+    with pytest.raises(ValueError, match="bad magic"):
+        PackedFile(bad)

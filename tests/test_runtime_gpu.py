@@ -179,3 +179,32 @@ def test_device_resident_images_fused_and_staged(tmp_path: Path) -> None:
         rt.end_step()
         rt.shutdown()
         store.close()
+
+
+def test_packed_image_file_source_streams_identically(tmp_path: Path) -> None:
+    """Export the slab as a packed-image file, stream a fresh model from it: same block images, same forward."""
+    from stagehand_b200.packed_file import export_packed_file
+
+    model, rt, x = _build("cfg1", tmp_path)
+    export_packed_file(rt, tmp_path / "cfg1.sqpk")
+    rt.shutdown()
+    kw, _tokens = CFGS["cfg1"]
+    torch.manual_seed(0)
+    fresh = TinyBlockModel(**kw)
+    for p in fresh.parameters():
+        p.requires_grad_(False)
+    cfg = sh.StagehandConfig(pinned_pool_mb=256, pinned_slab_mb=64, telemetry_enabled=False, nan_inf_check=False)
+    rt2 = sh.StagehandRuntime(fresh, cfg, block_pattern=BLOCK_PATTERNS["tiny"], dtype=torch.bfloat16, inference_mode=True)
+    assert rt2.convert_registry_to_file_backed(str(tmp_path / "cfg1.sqpk")) == int(G["cfg1__converted"])
+    rt2.begin_step(0)
+    with torch.inference_mode(), rt2.managed_forward():
+        y = fresh(x)
+    torch.cuda.synchronize()
+    digests = []
+    for entry in rt2._registry.blocks_in_order():
+        img = rt2._residency.get_entry(entry.block_id).gpu_tensor.view(torch.uint8).cpu().numpy()
+        digests.append(hashlib.sha256(img.tobytes()).hexdigest())
+    assert digests == [str(d) for d in G["cfg1__block_sha256"]]
+    assert _rel_l2(y, "cfg1") <= 1e-2
+    rt2.end_step()
+    rt2.shutdown()

@@ -531,7 +531,7 @@ def compose_line(args, world: int, results: dict, peaks: dict, link_peak: float,
                 "frac": achieved / peaks["hbm_gbs"],
                 "traffic": NCU_TRAFFIC_PER_ALGORITHMIC_BYTE * 3.0 * prof["elements"] / prof["launches"],
                 "traffic_source": "dram bytes read+written per launch, scaled by weights processed from the ncu capture "
-                                  "of a 151 M-weight launch (profiles/sq_block_kernel_12288x12288_ncu_full.md)",
+                                  "of a 151 M-weight launch (summary committed under profiles/)",
                 "peak_source": peaks["source"],
                 "launches": prof["launches"], "mean_launch_ms": prof["kernel_ms"] / prof["launches"],
                 "algorithmic_bytes_per_launch": 3.0 * prof["elements"] / prof["launches"]}

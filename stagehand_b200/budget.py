@@ -19,6 +19,15 @@ __all__ = ["BudgetManager"]
 _MB = 1024 * 1024
 
 
+def _allocated_bytes() -> int:
+    """``torch.cuda.memory_allocated()`` without flattening the allocator's whole statistics tree."""
+    try:
+        stats = torch._C._cuda_memoryStats(torch.cuda.current_device())
+        return int(stats["allocated_bytes"]["all"]["current"])
+    except Exception:
+        return int(torch.cuda.memory_allocated())
+
+
 class BudgetManager:
     def __init__(self, high_watermark_mb: int = 22000, low_watermark_mb: int = 18000) -> None:
         if high_watermark_mb <= low_watermark_mb:
@@ -46,7 +55,7 @@ class BudgetManager:
             return 0.0
         now = time.monotonic()
         if self._reading is None or now - self._reading[0] > self._reading_ttl_s:
-            self._reading = (now, torch.cuda.memory_allocated())
+            self._reading = (now, _allocated_bytes())
         used = self._reading[1]
         if self._credit_bytes is not None:
             used = max(0, used - int(self._credit_bytes()))

@@ -130,11 +130,10 @@ class PackedBlockImage:
         if not self.dynamic_rows:
             return False
         changed = False
-        live = dict(module.named_parameters()) if module is not None else {}
         for row in self.dynamic_rows:
             desc = self.descs[row.desc_index]
             source: torch.Tensor | None = None
-            param = live.get(row.name)
+            param = _find_param(module, row.name)
             if param is not None and param.data.numel() == row.numel:
                 source = param.data
                 if cache is not None and row.name not in cache:
@@ -196,6 +195,16 @@ class PackedBlockImage:
             d.src_off -= self.static_bytes
             dynamic.append(d)
         return self._static_split[0], self._static_split[1], _native.make_descs(dynamic), len(dynamic)
+
+
+def _find_param(module: nn.Module | None, dotted: str) -> nn.Parameter | None:
+    """``dict(module.named_parameters()).get(dotted)`` without enumerating every parameter."""
+    node: Any = module
+    for part in dotted.split("."):
+        if node is None:
+            return None
+        node = getattr(node, part, None)
+    return node if isinstance(node, nn.Parameter) else None
 
 
 def _flat_f32(t: torch.Tensor) -> torch.Tensor:

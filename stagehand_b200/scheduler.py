@@ -710,10 +710,11 @@ class StagehandScheduler:
                 self._restore_from_pooled_slab(block_id, module, res)
             else:
                 _restore_params_from_tensor(module, res.gpu_tensor.view(torch.uint8), res.param_layout)
-            target = res.gpu_tensor.device
-            for param in module.parameters():
-                if param.grad is not None and param.grad.device != target:
-                    param.grad = param.grad.to(target, non_blocking=True)
+            if not self._inference_mode:     # gradients exist only when training
+                target = res.gpu_tensor.device
+                for param in module.parameters():
+                    if param.grad is not None and param.grad.device != target:
+                        param.grad = param.grad.to(target, non_blocking=True)
         if res.host_slab is not None and not isinstance(res.host_slab, tuple):
             self._engine._pool.release(res.host_slab)
         res.host_slab = None

@@ -33,7 +33,8 @@ from stagehand_b200 import _native
 from stagehand_b200._native import (SH_DT_BF16, SH_DT_F16, SH_DT_F32, SH_KIND_CAST_F32, SH_KIND_COPY,
                                     SH_KIND_DEQUANT_I8, SH_KIND_ZERO, ShParamDesc)
 
-__all__ = ["PackedBlockImage", "plan_block_image", "runtime_dtype_code", "ALIGN_MATRIX", "ALIGN_VECTOR"]
+__all__ = ["PackedBlockImage", "plan_block_image", "plan_file_image", "runtime_dtype_code", "ALIGN_MATRIX",
+           "ALIGN_VECTOR"]
 
 ALIGN_MATRIX = 256   # start of every int8 matrix in the image
 ALIGN_VECTOR = 16    # start of every scale / zero-point / bias / dynamic vector (bulk-copy granularity)
@@ -60,6 +61,7 @@ class _StaticOp:
     nbytes: int
     tensor: torch.Tensor          # CPU tensor; 2-D int8 view for matrices, flat otherwise
     matrix: bool = False
+    cast_to: torch.dtype | None = None   # convert while copying (a file tensor stored in another dtype)
 
 
 @dataclass
@@ -112,6 +114,17 @@ class PackedBlockImage:
                     lib.sh_pack_rows(base + op.offset, cols, t.data_ptr(), int(t.stride(0)) * t.element_size(),
                                      rows, cols * t.element_size(), threads),
                     "sh_pack_rows")
+            elif op.cast_to is not None:
+                buffer[op.offset : op.offset + op.nbytes].view(op.cast_to).copy_(t.reshape(-1))
+            elif op.nbytes >= (8 << 20) and t.is_contiguous():
+                # a large flat region: split the host copy over threads in 4 KiB rows, then the tail
+                rows = op.nbytes // 4096
+                _native.check(lib.sh_pack_rows(base + op.offset, 4096, t.data_ptr(), 4096, rows, 4096, threads),
+                              "sh_pack_rows")
+                done = rows * 4096
+                if done < op.nbytes:
+                    raw = t.reshape(-1).view(torch.uint8)
+                    buffer[op.offset + done : op.offset + op.nbytes].copy_(raw[done:])
             else:
                 buffer[op.offset : op.offset + op.nbytes].view(t.dtype).copy_(t.reshape(-1))
 
@@ -307,6 +320,67 @@ def plan_block_image(
             desc = zero_desc(dst_off, numel)   # dynamic rows are rewritten at every staging
         rows.append(desc)
 
+    image.static_bytes = _round_up(cursor, ALIGN_MATRIX)
+    cursor = image.static_bytes
+    for name, index, numel, dst_off in pending_dynamic:
+        slot = _round_up(numel * 4, ALIGN_VECTOR)
+        image.dynamic_rows.append(_DynamicRow(name, index, cursor, slot, numel, dst_off))
+        rows[index].src_off = cursor
+        cursor += slot
+    image.total_bytes = max(_round_up(cursor, ALIGN_MATRIX), ALIGN_MATRIX)
+    image.descs = _native.make_descs(rows)
+    image.n_descs = len(rows)
+    return image
+
+
+def plan_file_image(
+    block_id: str,
+    param_layout: list[tuple[str, tuple[int, ...], torch.dtype, int, int]],
+    file_specs: Mapping[str, Any],
+    module_param_names: set[str],
+    tensor_view: Any,
+    module: nn.Module | None,
+    out_bytes: int,
+) -> PackedBlockImage:
+    """Image of a safetensors-backed block: file regions already in (or converted to) the runtime dtype.
+
+    Row by row as the reference stages such a block (``src/stagehand/scheduler.py:184-241``): a parameter
+    with a file spec is copied from its file region -- converted on the way when the file stores another
+    dtype --, a module-owned one is staged from the live module at every load, anything else is zero-filled.
+    *tensor_view(spec)* returns the CPU tensor view of a spec's file region.  Every static row is a ``COPY``
+    for the block kernel; the image is as large as the runtime-dtype slab (nothing is compressed), what it
+    buys is the page-locked image cache, the pooled VRAM slabs and the copy / expand pipeline.
+    """
+    if not param_layout:
+        raise ValueError(f"block {block_id!r} has no parameter layout")
+    runtime_dtype = param_layout[0][2]
+    runtime_dtype_code(runtime_dtype)
+    itemsize = runtime_dtype.itemsize
+    image = PackedBlockImage(block_id=block_id, runtime_dtype=runtime_dtype, out_bytes=out_bytes)
+    live_names = {n for n, _ in module.named_parameters()} if module is not None else set()
+    rows: list[ShParamDesc] = []
+    pending_dynamic: list[tuple[str, int, int, int]] = []
+    cursor = 0
+    for name, _shape, dtype, dst_off, numel in param_layout:
+        if dtype != runtime_dtype:
+            raise ValueError(f"block {block_id!r}: mixed runtime dtypes in one layout")
+        nbytes = numel * itemsize
+        spec = file_specs.get(name)
+        if spec is not None:
+            view = tensor_view(spec)
+            if view.numel() != numel:
+                raise ValueError(f"{block_id}.{name}: file tensor has {view.numel()} values, expected {numel}")
+            cursor = _round_up(cursor, ALIGN_MATRIX)
+            image.static_ops.append(_StaticOp(cursor, nbytes, view if view.is_contiguous() else view.contiguous(),
+                                              cast_to=None if view.dtype == runtime_dtype else runtime_dtype))
+            rows.append(ShParamDesc(kind=SH_KIND_COPY, flags=0, src_off=cursor, scale_off=0, zp_off=-1, dst_off=dst_off,
+                                    rows=1, cols=nbytes, ld=0))
+            cursor += nbytes
+            continue
+        if name in module_param_names and name in live_names:
+            pending_dynamic.append((name, len(rows), numel, dst_off))
+        rows.append(ShParamDesc(kind=SH_KIND_ZERO, flags=0, src_off=0, scale_off=0, zp_off=-1, dst_off=dst_off,
+                                rows=1, cols=nbytes, ld=0))
     image.static_bytes = _round_up(cursor, ALIGN_MATRIX)
     cursor = image.static_bytes
     for name, index, numel, dst_off in pending_dynamic:

@@ -442,7 +442,8 @@ class StagehandScheduler:
             self._load_module_backed_direct(block_id, entry, res)
             return
 
-        if entry.squareq_backed:
+        if entry.squareq_backed or (entry.file_backed and torch.cuda.is_available()):
+            # packed-image path: SquareQ blocks always; safetensors-backed blocks whenever there is a GPU
             self._load_squareq_block(block_id, entry, res, state)
             return
 
@@ -482,7 +483,7 @@ class StagehandScheduler:
         largest = 0
         largest_dyn = 0
         for e in self._ordered_blocks:
-            if e.squareq_backed:
+            if e.squareq_backed or e.file_backed:
                 plan = self._image_plan(e)
                 largest = max(largest, plan.total_bytes)
                 largest_dyn = max(largest_dyn, plan.total_bytes - plan.static_bytes)
@@ -505,6 +506,16 @@ class StagehandScheduler:
             from stagehand_b200.packed import plan_block_image
 
             source = str(entry.source_path)
+            if not entry.squareq_backed:
+                from stagehand_b200.packed import plan_file_image
+
+                plan = plan_file_image(
+                    entry.block_id, list(entry.param_layout), {s.param_name: s for s in entry.file_param_specs},
+                    set(entry.module_param_names),
+                    lambda spec: self._get_file_tensor_view(spec.file_path or source, spec),
+                    entry.module_ref(), entry.size_bytes)
+                self._image_plans[entry.block_id] = plan
+                return plan
             if entry.source_format == "squareq_packed":
                 plan = self._packed_file(source).image_plan(entry.block_id)
                 if plan.out_bytes != entry.size_bytes or plan.runtime_dtype != entry.dtype:

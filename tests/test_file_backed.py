@@ -143,3 +143,24 @@ def test_training_step_with_trainable_adapters(tmp_path: Path) -> None:
         assert torch.allclose(got_blk.lora_a.grad.cpu(), ref_blk.lora_a.grad, atol=1e-5, rtol=1e-4)
         assert torch.allclose(got_blk.lora_b.grad.cpu(), ref_blk.lora_b.grad, atol=1e-5, rtol=1e-4)
     rt.shutdown()
+
+
+# ── the same scenarios on a GPU: safetensors-backed blocks go through the packed-image path ──────────
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("sharded", [False, True])
+def test_gpu_file_backed_blocks_stream_through_the_block_kernel(sharded: bool, tmp_path: Path) -> None:
+    from stagehand_b200 import _native
+
+    before = _native.stats()["kernel_launches"]
+    test_file_backed_forward_matches_resident_model(sharded, tmp_path)
+    assert _native.stats()["kernel_launches"] - before >= 8      # 4 blocks x 2 steps under a tight budget
+
+
+@pytest.mark.gpu
+def test_gpu_file_dtype_cast_and_training(tmp_path: Path) -> None:
+    (tmp_path / "a").mkdir()
+    (tmp_path / "b").mkdir()
+    test_file_dtype_is_cast_to_the_runtime_dtype(tmp_path / "a")
+    test_training_step_with_trainable_adapters(tmp_path / "b")

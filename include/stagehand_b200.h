@@ -246,6 +246,49 @@ int32_t sh_profile_enable(int32_t on);
 int32_t sh_profile_collect(double* kernel_ms_out, int64_t* launches_out, int64_t* elements_out,
                            int64_t* bytes_out, int32_t timeout_ms);
 
+/* ── VRAM slab allocator on CUDA virtual memory management ───────────── */
+
+typedef struct ShVmmStats {
+    int64_t total_slabs;
+    int64_t total_regions;
+    int64_t mapped_regions;
+    int64_t mapped_bytes;
+    int64_t vram_ceiling;
+    int64_t granularity;
+    int64_t evictions;
+} ShVmmStats;
+
+/*
+ * Address space is reserved once per slab; physical memory is mapped per region on demand and
+ * unmapped again (lowest slab priority first, then least recently used, never a held region, never
+ * before the region's release event has completed) to stay under a byte ceiling.  A request that does
+ * not fit and finds nothing evictable fails with SH_ERR_OOM; waits are bounded (SH_ERR_TIMEOUT).
+ * Failure text: sh_vmm_last_error.
+ *
+ * Replaces the reference's SlabAllocator (vmm_src/python.rs:44-135, vmm_src/allocator.rs:80-533):
+ *   sh_vmm_create           SlabAllocator(device, ceiling_mb)      python.rs:44-52  (ceiling 0 = 90 % of the device)
+ *   sh_vmm_create_slab      create_slab(total_size)                python.rs:54-56
+ *   sh_vmm_define_region    define_region(slab, offset, size)      python.rs:58-64
+ *   sh_vmm_ensure_resident  ensure_resident(slab, region, stream)  python.rs:66-80  (hold = 1)
+ *                           prefetch(slab, region)                 python.rs:82-85  (hold = 0: map, do not hold)
+ *   sh_vmm_release          ResidentHandle.release / drop          vmm_src/handle.rs:65-110 (records an event on `stream`)
+ *   sh_vmm_set_priority     set_priority(slab, priority)           python.rs:87-89
+ *   sh_vmm_set_ceiling      set_vram_ceiling(bytes)                python.rs:91-94
+ *   sh_vmm_destroy_slab     destroy_slab(slab)                     python.rs:96-98 (SH_ERR_BUSY while a region is held)
+ *   sh_vmm_stats            stats()                                python.rs:100-121
+ */
+int32_t sh_vmm_create(int32_t device, uint64_t ceiling_bytes, uint64_t* allocator_out);
+int32_t sh_vmm_destroy(uint64_t allocator);
+int32_t sh_vmm_create_slab(uint64_t allocator, uint64_t total_bytes, int32_t* slab_out);
+int32_t sh_vmm_define_region(uint64_t allocator, int32_t slab, uint64_t offset, uint64_t size, int32_t* region_out);
+int32_t sh_vmm_ensure_resident(uint64_t allocator, int32_t slab, int32_t region, int32_t hold, void** dev_ptr_out);
+int32_t sh_vmm_release(uint64_t allocator, int32_t slab, int32_t region, uint64_t stream);
+int32_t sh_vmm_set_priority(uint64_t allocator, int32_t slab, uint32_t priority);
+int32_t sh_vmm_set_ceiling(uint64_t allocator, uint64_t ceiling_bytes);
+int32_t sh_vmm_destroy_slab(uint64_t allocator, int32_t slab);
+int32_t sh_vmm_stats(uint64_t allocator, ShVmmStats* out);
+int32_t sh_vmm_last_error(char* buf, int32_t buf_len);
+
 /*
  * Host image -> runtime-dtype weights in VRAM for callers that cannot allocate device memory on this
  * path (a process whose GPU memory was handed to another allocator at start-up, a plug-in that must

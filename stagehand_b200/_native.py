@@ -44,6 +44,13 @@ class ShDeviceInfo(ctypes.Structure):
     ]
 
 
+class ShVmmStats(ctypes.Structure):
+    _fields_ = [
+        ("total_slabs", c_int64), ("total_regions", c_int64), ("mapped_regions", c_int64), ("mapped_bytes", c_int64),
+        ("vram_ceiling", c_int64), ("granularity", c_int64), ("evictions", c_int64),
+    ]
+
+
 class ShStats(ctypes.Structure):
     _fields_ = [
         ("kernel_launches", c_int64), ("elements_dequantised", c_int64),
@@ -93,6 +100,17 @@ _SIGNATURES: dict[str, list] = {
     "sh_dequant_from_host_noalloc": [_P_DESC, c_int32, c_void_p, c_size_t, c_void_p, c_size_t, c_int32, c_uint64,
                                      c_void_p],
     "sh_noalloc_last_error": [c_char_p, c_int32],
+    "sh_vmm_create": [c_int32, c_uint64, POINTER(c_uint64)],
+    "sh_vmm_destroy": [c_uint64],
+    "sh_vmm_create_slab": [c_uint64, c_uint64, POINTER(c_int32)],
+    "sh_vmm_define_region": [c_uint64, c_int32, c_uint64, c_uint64, POINTER(c_int32)],
+    "sh_vmm_ensure_resident": [c_uint64, c_int32, c_int32, c_int32, POINTER(c_void_p)],
+    "sh_vmm_release": [c_uint64, c_int32, c_int32, c_uint64],
+    "sh_vmm_set_priority": [c_uint64, c_int32, c_uint32],
+    "sh_vmm_set_ceiling": [c_uint64, c_uint64],
+    "sh_vmm_destroy_slab": [c_uint64, c_int32],
+    "sh_vmm_stats": [c_uint64, POINTER(ShVmmStats)],
+    "sh_vmm_last_error": [c_char_p, c_int32],
     "sh_profile_enable": [c_int32],
     "sh_profile_collect": [POINTER(c_double), POINTER(c_int64), POINTER(c_int64), POINTER(c_int64), c_int32],
 }

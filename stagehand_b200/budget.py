@@ -36,6 +36,7 @@ class BudgetManager:
         self._high_watermark_mb = high_watermark_mb
         self._low_watermark_mb = low_watermark_mb
         self._credit_bytes: Callable[[], int] | None = None
+        self._external_bytes: Callable[[], int] | None = None
         # torch.cuda.memory_allocated() assembles the allocator's whole statistics table on every call
         # (tens of microseconds); the scheduler asks several times per block, so the reading is reused
         # for a short time.  invalidate() drops it (the device pool calls it when it really allocates).
@@ -45,6 +46,10 @@ class BudgetManager:
     def set_reusable_bytes_source(self, fn: Callable[[], int] | None) -> None:
         """Register a callable returning allocator-visible bytes that are free for reuse."""
         self._credit_bytes = fn
+
+    def set_external_bytes_source(self, fn: Callable[[], int] | None) -> None:
+        """Register a callable returning VRAM in use that the torch allocator does not see."""
+        self._external_bytes = fn
 
     def invalidate(self) -> None:
         """Forget the cached allocator reading (call after a large allocation or free)."""
@@ -57,6 +62,8 @@ class BudgetManager:
         if self._reading is None or now - self._reading[0] > self._reading_ttl_s:
             self._reading = (now, _allocated_bytes())
         used = self._reading[1]
+        if self._external_bytes is not None:
+            used += int(self._external_bytes())
         if self._credit_bytes is not None:
             used = max(0, used - int(self._credit_bytes()))
         return used / _MB

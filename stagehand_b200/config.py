@@ -55,3 +55,7 @@ class StagehandConfig:
     device_staging_slabs: int = 0
     # Host threads used to pack an image that is not cached.
     pack_threads: int = 8
+    # Where the block slabs in VRAM come from: "torch" (caching allocator) or "vmm" (the C++ virtual-memory
+    # slab allocator: parked slabs can be unmapped under `vmm_ceiling_mb` without fragmenting anything).
+    device_pool_backend: str = "torch"
+    vmm_ceiling_mb: int = 0      # 0 = 90 % of the device

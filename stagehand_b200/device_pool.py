@@ -19,7 +19,7 @@ from typing import Any
 
 import torch
 
-__all__ = ["DeviceSlab", "DeviceSlabPool", "StagingRing"]
+__all__ = ["DeviceSlab", "DeviceSlabPool", "VmmDeviceSlabPool", "StagingRing"]
 
 
 @dataclass
@@ -28,6 +28,8 @@ class DeviceSlab:
     nbytes: int
     last_use: Any = None              # events.Event recorded after the last reader / writer was queued
     slab_id: int = -1
+    vmm_slab: int = -1                # virtual-memory backend: the allocator's slab id and the held handle
+    handle: Any = None
 
 
 class DeviceSlabPool:
@@ -125,3 +127,86 @@ class StagingRing:
 
     def total_bytes(self) -> int:
         return self.slab_bytes * len(self._slabs)
+
+
+class VmmDeviceSlabPool:
+    """Same interface as :class:`DeviceSlabPool`, backed by the C++ virtual-memory slab allocator.
+
+    Every slab is a region of reserved address space; parked slabs stay mapped (and are reused without
+    any driver call) until the allocator's byte ceiling makes it unmap the least recently used ones --
+    so VRAM parked here can be handed back without fragmenting anything, and several runtimes given the
+    same allocator share one ceiling.  The memory is not the torch allocator's: the budget manager is
+    told about it through :meth:`mapped_bytes`.
+    """
+
+    def __init__(self, device: torch.device | str = "cuda", allocator=None, ceiling_mb: int | None = None,
+                 on_allocation=None, on_trim=None) -> None:
+        from stagehand_b200.vmm import SlabAllocator
+
+        self._device = torch.device(device)
+        index = self._device.index if self._device.index is not None else torch.cuda.current_device()
+        self._owns_allocator = allocator is None
+        self._allocator = allocator if allocator is not None else SlabAllocator(index, ceiling_mb)
+        self._free: dict[int, list[DeviceSlab]] = {}
+        self._parked_bytes = 0
+        self._on_allocation, self._on_trim = on_allocation, on_trim
+        self._next_id = 0
+        self.allocations = 0
+        self.reuses = 0
+
+    def acquire(self, nbytes: int) -> DeviceSlab:
+        from stagehand_b200.events import acquire_event
+
+        bucket = self._free.get(nbytes)
+        if bucket:
+            slab = bucket.pop()
+            self._parked_bytes -= slab.nbytes
+            slab.handle = self._allocator.ensure_resident(slab.vmm_slab, 0)   # re-maps it if it was evicted
+            if slab.handle.ptr != slab.tensor.data_ptr():
+                raise RuntimeError("a region's address changed across a remap")
+            self.reuses += 1
+            return slab
+        vmm_slab = self._allocator.create_slab(nbytes)
+        self._allocator.define_region(vmm_slab, 0, nbytes)
+        handle = self._allocator.ensure_resident(vmm_slab, 0)
+        self._next_id += 1
+        slab = DeviceSlab(tensor=handle.as_tensor(torch.uint8, [nbytes]), nbytes=nbytes, slab_id=self._next_id)
+        slab.vmm_slab, slab.handle = vmm_slab, handle
+        slab.last_use = acquire_event().record(torch.cuda.current_stream(self._device))
+        self.allocations += 1
+        if self._on_allocation is not None:
+            self._on_allocation()
+        return slab
+
+    def release(self, slab: DeviceSlab, stream: torch.cuda.Stream | None = None) -> None:
+        from stagehand_b200.events import acquire_event, release_event
+
+        s = stream if stream is not None else torch.cuda.current_stream(self._device)
+        release_event(slab.last_use)
+        slab.last_use = acquire_event().record(s)
+        slab.handle.release(s.cuda_stream)          # evictable once the work queued on `s` so far has finished
+        slab.handle = None
+        self._free.setdefault(slab.nbytes, []).append(slab)
+        self._parked_bytes += slab.nbytes
+
+    def reusable_bytes(self) -> int:
+        return self._parked_bytes
+
+    def mapped_bytes(self) -> int:
+        return int(self._allocator.stats()["mapped_bytes"])
+
+    def trim(self) -> None:
+        if self._on_trim is not None:
+            self._on_trim()
+        for bucket in self._free.values():
+            for slab in bucket:
+                self._allocator.destroy_slab(slab.vmm_slab)
+        self._free.clear()
+        self._parked_bytes = 0
+        if self._on_allocation is not None:
+            self._on_allocation()
+
+    def close(self) -> None:
+        self.trim()
+        if self._owns_allocator:
+            self._allocator.close()

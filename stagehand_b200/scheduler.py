@@ -330,7 +330,24 @@ class StagehandScheduler:
             self._image_store.close()
             self._image_store = None
         if self._device_pool is not None:
-            self._device_pool.trim()
+            if hasattr(self._device_pool, "close"):
+                # Virtual-memory backend: closing unmaps the slabs, so no parameter may keep pointing into
+                # them.  Blocks still on the device are evicted the normal way first (parameters emptied or
+                # moved to the host), in-flight ones are completed and then evicted.
+                for block_id in self._block_ids:
+                    state = self._residency.get_state(block_id)
+                    if state is BlockState.PREFETCHING:
+                        self._await_pending(block_id)
+                        self._finalize_gpu_load(block_id)
+                        state = BlockState.GPU_READY
+                    if state is BlockState.GPU_READY and self._residency.get_entry(block_id).device_slab is not None:
+                        self._residency.get_entry(block_id).refcount = 0
+                        self._evict_block(block_id, save_back=not self._inference_mode)
+                torch.cuda.synchronize()
+                self._view_cache.clear()
+                self._device_pool.close()
+            else:
+                self._device_pool.trim()
         self._image_plans.clear()
         for packed in self._packed_files.values():
             packed.close()
@@ -474,8 +491,16 @@ class StagehandScheduler:
         device = torch.device("cuda", torch.cuda.current_device())
         n_staging = self._config.device_staging_slabs or (self._policy.prefetch_window + 1)
         self._streamer = Int8BlockStreamer(device, self._engine.copy_stream, n_staging)
-        self._device_pool = DeviceSlabPool(device, on_allocation=getattr(self._budget, "invalidate", None),
-                                           on_trim=self._view_cache.clear)
+        pool_kw = dict(on_allocation=getattr(self._budget, "invalidate", None), on_trim=self._view_cache.clear)
+        if getattr(self._config, "device_pool_backend", "torch") == "vmm":
+            from stagehand_b200.device_pool import VmmDeviceSlabPool
+
+            self._device_pool = VmmDeviceSlabPool(device, ceiling_mb=int(getattr(self._config, "vmm_ceiling_mb", 0)) or None,
+                                                  **pool_kw)
+            if hasattr(self._budget, "set_external_bytes_source"):
+                self._budget.set_external_bytes_source(self._device_pool.mapped_bytes)
+        else:
+            self._device_pool = DeviceSlabPool(device, **pool_kw)
         if hasattr(self._budget, "set_reusable_bytes_source"):
             self._budget.set_reusable_bytes_source(self._device_pool.reusable_bytes)
         self._image_store = ImageStore(self._image_cache_budget(), pinned=True)

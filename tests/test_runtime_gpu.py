@@ -208,3 +208,24 @@ def test_packed_image_file_source_streams_identically(tmp_path: Path) -> None:
     assert _rel_l2(y, "cfg1") <= 1e-2
     rt2.end_step()
     rt2.shutdown()
+
+
+def test_virtual_memory_slab_backend(tmp_path: Path) -> None:
+    """VRAM slabs from the C++ virtual-memory allocator instead of the torch allocator: same results, and
+    the budget manager still sees the memory (eviction keeps working under a tight budget)."""
+    model, rt, x = _build("cfg1", tmp_path, device_pool_backend="vmm", vram_high_watermark_mb=60,
+                          vram_low_watermark_mb=30, prefetch_window_blocks=1)
+    outs = []
+    for step in range(3):
+        rt.begin_step(step)
+        with torch.inference_mode(), rt.managed_forward():
+            outs.append(model(x))
+        rt.end_step()
+    torch.cuda.synchronize()
+    assert all(_rel_l2(y, "cfg1") <= 1e-2 for y in outs) and torch.equal(outs[0], outs[2])
+    pool = rt._scheduler._device_pool
+    assert type(pool).__name__ == "VmmDeviceSlabPool" and pool.mapped_bytes() >= 25_000_000
+    assert rt.telemetry.last().evictions >= 2 and pool.reuses > 0
+    assert rt._budget.vram_used_mb() >= 24                    # the mapped slabs count although torch did not allocate them
+    rt.shutdown()
+    assert all(b.qkv.weight.numel() == 0 for b in model.blocks)   # nothing points into unmapped memory

@@ -262,7 +262,7 @@ def measured_peaks() -> dict:
 # ── CPU baseline / reference arm ─────────────────────────────────────────
 
 
-def cpu_dequant_sample(min_seconds: float, max_reps: int, pinned: bool):
+def cpu_dequant_sample(min_seconds: float, max_reps: int, pinned: bool, warmup: int = 1, exact_reps: int = 0):
     """Time the reference's host dequant (oracle/torch_port.py: same ATen ops, all host threads).
 
     Sample = the three weights of one Flux-shaped single-stream block (141.6 M int8 weights ->
@@ -279,17 +279,19 @@ def cpu_dequant_sample(min_seconds: float, max_reps: int, pinned: bool):
     weights = [synth_squareq_layer(o, i, g, has_bias=False) for o, i in shapes]
     out_bytes = sum(o * i for o, i in shapes) * 2
     slab = torch.empty(out_bytes, dtype=torch.uint8, pin_memory=pinned)
-    host_stage_weights(slab, weights)                      # warm-up (page faults, thread pool)
+    for _ in range(max(warmup, 1)):
+        host_stage_weights(slab, weights)                  # warm-up (page faults, thread pool)
     times = []
     t_all = time.perf_counter()
-    while len(times) < max_reps and (len(times) < 2 or time.perf_counter() - t_all < min_seconds):
+    while (len(times) < exact_reps) if exact_reps else (
+            len(times) < max_reps and (len(times) < 2 or time.perf_counter() - t_all < min_seconds)):
         t0 = time.perf_counter()
         host_stage_weights(slab, weights)
         times.append(time.perf_counter() - t0)
-    sec = statistics.median(times)
+    sec = (sum(times) / len(times)) if exact_reps else statistics.median(times)
     desc = (f"one Flux-shaped single-stream block (mod 9216x3072, lin1 21504x3072, lin2 3072x15360 = "
             f"{out_bytes // 2 / 1e6:.1f} M weights) dequantised to bf16 into a {'pinned' if pinned else 'pageable'} "
-            f"slab, median of {len(times)} repetitions")
+            f"slab, {'mean' if exact_reps else 'median'} of {len(times)} repetitions")
     return out_bytes / sec / 1e9, sec * 1e3, desc, torch.get_num_threads()
 
 
@@ -300,13 +302,13 @@ def run_reference_arm(args) -> None:
     import torch
 
     pinned = torch.cuda.is_available()
-    reps = max(1, args.steps)
-    # warm-up repetitions are folded into the sampler (it always discards its first pass)
-    gbs, ms, desc, threads = cpu_dequant_sample(min_seconds=5.0 * max(1, args.warmup), max_reps=max(reps, 3), pinned=pinned)
+    # W untimed samples, then exactly K timed ones (each sample = one step of the bounded workload)
+    gbs, ms, desc, threads = cpu_dequant_sample(min_seconds=0.0, max_reps=0, pinned=pinned, warmup=args.warmup,
+                                                exact_reps=max(1, args.steps))
     line = {
         "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic",
+        "dtype": "f32", "data": "synthetic",
         "config": {"workload": "flux1-dev-shaped DiT 19 double + 38 single blocks, hidden 3072, 4096+512 tokens, "
                                "SquareQ INT8 per-channel", "sample": desc,
                    "note": "host dequant only (scheduler.py:243-325 restated with the same ATen ops); the reference "
@@ -539,8 +541,8 @@ def compose_line(args, world: int, results: dict, peaks: dict, link_peak: float,
     line = {
         "metric": METRIC, "value": gbs(v["ms_total"]), "unit": UNIT, "n_gpus": world, "steps": K,
         "warmup": args.warmup, "ms_per_step": v["ms_total"] / K, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": v["desc"]["workload"], "vram_budget_gb": args.vram_budget_gb,
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": v["desc"]["workload"], "arithmetic": "int8 -> fp32 (subtract, multiply) -> bf16, round to nearest even", "vram_budget_gb": args.vram_budget_gb,
                    "prefetch_k": args.prefetch_k, "int8_elements_per_forward": v["desc"]["int8_elements"],
                    "l2": "inputs larger than L2 (11.8 GB of INT8 per step); no flush",
                    "value_source": "INT8 images resident in HBM" + ("" if world == 1 else

@@ -378,7 +378,10 @@ __global__ void __launch_bounds__(kThreads, SQ_MIN_CTAS_PER_SM) sq_block_kernel(
     __shared__ alignas(16) float s_zp[kSmemRows];
     __shared__ alignas(8) uint64_t s_bar;
 
-    const uint32_t tile = blockIdx.x;
+    const uint32_t tile = plan.tile_stride == 1u
+                              ? blockIdx.x
+                              : static_cast<uint32_t>((static_cast<uint64_t>(blockIdx.x) * plan.tile_stride) %
+                                                      static_cast<uint32_t>(plan.total_tiles));
     // descriptor of this tile: the last d with tile_begin[d] <= tile (binary search, uniform across the CTA)
     int d = 0;
     for (int hi = plan.n_desc; hi - d > 1;) {
@@ -430,6 +433,30 @@ static inline bool aligned(const void* p, uintptr_t a) { return (reinterpret_cas
 
 static inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
+static uint32_t gcd_u32(uint32_t a, uint32_t b) {
+    while (b != 0) {
+        const uint32_t t = a % b;
+        a = b;
+        b = t;
+    }
+    return a;
+}
+
+// Finishes a plan: total tile count and the CTA -> tile stride.  Launches that read another GPU's memory
+// use a stride near total / golden ratio (coprime with total, so the mapping is a permutation).
+static void close_plan(BlockPlan& plan, uint32_t tiles) {
+    plan.tile_begin[plan.n_desc] = tiles;
+    plan.total_tiles = static_cast<int32_t>(tiles);
+    plan.tile_stride = 1;
+    bool remote = false;
+    for (int i = 0; i < plan.n_desc; ++i) remote = remote || (plan.d[i].flags & SH_DESC_PEER_SOURCE) != 0;
+    if (remote && tiles > 64) {
+        uint32_t stride = static_cast<uint32_t>(static_cast<double>(tiles) * 0.6180339887);
+        while (stride > 1 && gcd_u32(stride, tiles) != 1) --stride;
+        plan.tile_stride = stride > 1 ? stride : 1;
+    }
+}
+
 int build_plans(const ShParamDesc* descs, int n, const void* packed, size_t packed_bytes, void* out,
                 size_t out_bytes, int out_dtype, BlockPlan* plans_out, int* n_plans_out, int64_t* elements_out,
                 int64_t* traffic_bytes_out, char* err, size_t err_len) {
@@ -450,10 +477,7 @@ int build_plans(const ShParamDesc* descs, int n, const void* packed, size_t pack
     for (int i = 0; i < n; ++i) {
         const ShParamDesc& u = descs[i];
         if (plan == nullptr || plan->n_desc == kMaxDescs) {
-            if (plan != nullptr) {
-                plan->tile_begin[plan->n_desc] = tiles;
-                plan->total_tiles = static_cast<int32_t>(tiles);
-            }
+            if (plan != nullptr) close_plan(*plan, tiles);
             plan = &plans_out[n_plans++];
             memset(plan, 0, sizeof(BlockPlan));
             tiles = 0;
@@ -564,10 +588,7 @@ int build_plans(const ShParamDesc* descs, int n, const void* packed, size_t pack
         plan->n_desc += 1;
         tiles += static_cast<uint32_t>(n_tiles);
     }
-    if (plan != nullptr) {
-        plan->tile_begin[plan->n_desc] = tiles;
-        plan->total_tiles = static_cast<int32_t>(tiles);
-    }
+    if (plan != nullptr) close_plan(*plan, tiles);
     *n_plans_out = n_plans;
     if (elements_out) *elements_out = elements;
     if (traffic_bytes_out) *traffic_bytes_out = traffic;

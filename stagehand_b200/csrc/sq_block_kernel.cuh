@@ -70,6 +70,10 @@ struct DescDev {
 struct BlockPlan {
     int32_t  n_desc;
     int32_t  total_tiles;
+    uint32_t tile_stride;                 // CTA b works on tile (b * tile_stride) mod total_tiles; 1 = in order.
+    uint32_t pad_;                        // A stride coprime with total_tiles scatters neighbouring CTAs over the
+                                          // whole launch, so a launch that reads from several GPUs pulls from all
+                                          // of them at once instead of one stripe (one peer) at a time.
     uint32_t tile_begin[kMaxDescs + 1];   // first tile of each descriptor; [n_desc] = total
     DescDev  d[kMaxDescs];
 };

@@ -590,8 +590,8 @@ class StagehandScheduler:
                 slab = pool.acquire(plan.total_bytes)
             image = HostImage(buffer=slab.buffer[: plan.total_bytes], nbytes=plan.total_bytes,
                               pinned=torch.cuda.is_available())
-        else:
-            self._telemetry.record_image_cache_hit() if image.static_ready else None
+        elif image.static_ready:
+            self._telemetry.record_image_cache_hit()
         if not image.static_ready:
             plan.fill_static(image.buffer, threads=int(getattr(self._config, "pack_threads", 8)))
             image.static_ready = True

@@ -246,6 +246,42 @@ int32_t sh_profile_enable(int32_t on);
 int32_t sh_profile_collect(double* kernel_ms_out, int64_t* launches_out, int64_t* elements_out,
                            int64_t* bytes_out, int32_t timeout_ms);
 
+/* ── slot-rotation transfer engine ───────────────────────────────────── */
+
+/*
+ * Every registered block is kept in page-locked host memory; a window of GPU slots (memory owned by
+ * the caller, handed in with sh_turbo_set_slot_gpu_ptrs) holds the blocks around the one computing.
+ * sh_turbo_step(block, direction) = make `block` resident (the caller's stream is ordered after its
+ * copy), write the previous block back asynchronously, start copying the next one.  All waits are
+ * bounded by timeout_ms.  Failure text: sh_turbo_last_error.  Locations: 0 cpu, 1 gpu, 2 h2d, 3 d2h.
+ *
+ * Replaces the reference's TransferEngine (turbo_src/lib.rs:19-119, turbo_src/engine.rs:67-415):
+ *   sh_turbo_create / destroy     TransferEngine::new / Drop          engine.rs:67-80, :396-415
+ *   sh_turbo_register_block       register_block(param_sizes)         engine.rs:82-100
+ *   sh_turbo_initialize           initialize(device, window_size)     engine.rs:102-157
+ *   sh_turbo_stage_block          stage_block(idx, src_ptrs)          engine.rs:159-176
+ *   sh_turbo_set_slot_gpu_ptrs    set_slot_gpu_ptrs(slot, ptrs)       engine.rs:361-373
+ *   sh_turbo_step                 step(idx, "forward"|"backward")     engine.rs:304-341 (backward = 1)
+ *   sh_turbo_evict_sync           evict_sync(idx)                     engine.rs:298-302
+ *   sh_turbo_ptr                  gpu_ptr / cpu_ptr(block, param)     engine.rs:344-359 (on_gpu = 1 / 0)
+ *   sh_turbo_block_state          block_location / block_slot         engine.rs:375-394 (slot -1 = none)
+ *   sh_turbo_counts               num_blocks / num_gpu_slots / num_free_slots   engine.rs:380-382
+ *   sh_turbo_drain                drain()                             lib.rs:107-118
+ */
+int32_t sh_turbo_create(uint64_t* engine_out);
+int32_t sh_turbo_destroy(uint64_t engine);
+int32_t sh_turbo_register_block(uint64_t engine, const uint64_t* param_sizes, int32_t n_params, int32_t* block_out);
+int32_t sh_turbo_initialize(uint64_t engine, int32_t device, int32_t window_size);
+int32_t sh_turbo_stage_block(uint64_t engine, int32_t block, const uint64_t* src_ptrs, int32_t n_ptrs);
+int32_t sh_turbo_set_slot_gpu_ptrs(uint64_t engine, int32_t slot, const uint64_t* ptrs, int32_t n_ptrs);
+int32_t sh_turbo_step(uint64_t engine, int32_t block, int32_t backward, uint64_t caller_stream, int32_t timeout_ms);
+int32_t sh_turbo_evict_sync(uint64_t engine, int32_t block, uint64_t caller_stream, int32_t timeout_ms);
+int32_t sh_turbo_ptr(uint64_t engine, int32_t block, int32_t param, int32_t on_gpu, uint64_t* ptr_out);
+int32_t sh_turbo_block_state(uint64_t engine, int32_t block, int32_t* location_out, int32_t* slot_out);
+int32_t sh_turbo_counts(uint64_t engine, int32_t* blocks_out, int32_t* slots_out, int32_t* free_out);
+int32_t sh_turbo_drain(uint64_t engine, int32_t timeout_ms);
+int32_t sh_turbo_last_error(char* buf, int32_t buf_len);
+
 /* ── VRAM slab allocator on CUDA virtual memory management ───────────── */
 
 typedef struct ShVmmStats {

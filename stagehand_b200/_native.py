@@ -100,6 +100,19 @@ _SIGNATURES: dict[str, list] = {
     "sh_dequant_from_host_noalloc": [_P_DESC, c_int32, c_void_p, c_size_t, c_void_p, c_size_t, c_int32, c_uint64,
                                      c_void_p],
     "sh_noalloc_last_error": [c_char_p, c_int32],
+    "sh_turbo_create": [POINTER(c_uint64)],
+    "sh_turbo_destroy": [c_uint64],
+    "sh_turbo_register_block": [c_uint64, POINTER(c_uint64), c_int32, POINTER(c_int32)],
+    "sh_turbo_initialize": [c_uint64, c_int32, c_int32],
+    "sh_turbo_stage_block": [c_uint64, c_int32, POINTER(c_uint64), c_int32],
+    "sh_turbo_set_slot_gpu_ptrs": [c_uint64, c_int32, POINTER(c_uint64), c_int32],
+    "sh_turbo_step": [c_uint64, c_int32, c_int32, c_uint64, c_int32],
+    "sh_turbo_evict_sync": [c_uint64, c_int32, c_uint64, c_int32],
+    "sh_turbo_ptr": [c_uint64, c_int32, c_int32, c_int32, POINTER(c_uint64)],
+    "sh_turbo_block_state": [c_uint64, c_int32, POINTER(c_int32), POINTER(c_int32)],
+    "sh_turbo_counts": [c_uint64, POINTER(c_int32), POINTER(c_int32), POINTER(c_int32)],
+    "sh_turbo_drain": [c_uint64, c_int32],
+    "sh_turbo_last_error": [c_char_p, c_int32],
     "sh_vmm_create": [c_int32, c_uint64, POINTER(c_uint64)],
     "sh_vmm_destroy": [c_uint64],
     "sh_vmm_create_slab": [c_uint64, c_uint64, POINTER(c_int32)],

@@ -13,7 +13,7 @@ from pathlib import Path
 PKG_DIR = Path(__file__).resolve().parent
 LIB_PATH = PKG_DIR / "libstagehand_b200.so"
 SOURCES = [PKG_DIR / "csrc" / "sq_block_kernel.cu", PKG_DIR / "csrc" / "sh_capi.cu", PKG_DIR / "csrc" / "sh_noalloc.cu",
-           PKG_DIR / "csrc" / "sh_vmm.cu"]
+           PKG_DIR / "csrc" / "sh_vmm.cu", PKG_DIR / "csrc" / "sh_turbo.cu"]
 HEADERS = [PKG_DIR / "csrc" / "sq_block_kernel.cuh", PKG_DIR.parent / "include" / "stagehand_b200.h"]
 
 NVCC_FLAGS = [

@@ -1,0 +1,228 @@
+"""Slot-rotation block swapping on the C++ engine in ``csrc/sh_turbo.cu``.
+
+``TransferEngine`` has the methods of the reference's PyO3 class (``turbo_src/lib.rs:19-119``);
+``TurboConductor`` has the surface of the reference's wrapper (``src/stagehand/turbo.py:28-201``): every
+block's parameters live in page-locked host memory owned by the engine, a window of three GPU slots made
+of torch tensors holds the blocks around the current one, ``before_block`` / ``after_block`` swap
+``param.data`` between the slot views and the host views.
+"""
+from __future__ import annotations
+
+import ctypes
+import logging
+import re
+
+import torch
+from torch import nn
+
+from stagehand_b200 import _native
+
+__all__ = ["TransferEngine", "TurboConductor", "is_available"]
+
+log = logging.getLogger(__name__)
+_LOCATIONS = ("cpu", "gpu", "h2d", "d2h")
+
+
+def is_available() -> bool:
+    return torch.cuda.is_available() and _native.is_built()
+
+
+def _check(status: int, what: str) -> None:
+    if status == _native.SH_OK:
+        return
+    buf = ctypes.create_string_buffer(256)
+    _native.lib().sh_turbo_last_error(buf, 256)
+    text = f"{what}: {buf.value.decode('utf-8', 'replace')}"
+    if status == _native.SH_ERR_INVALID_ARG:
+        raise ValueError(text)
+    raise RuntimeError(f"{text} (status {status})")
+
+
+def _u64_array(values) -> ctypes.Array:
+    return (ctypes.c_uint64 * max(len(values), 1))(*[int(v) for v in values])
+
+
+class TransferEngine:
+    def __init__(self, wait_timeout_ms: int = 120_000) -> None:
+        self._lib = _native.lib()
+        out = ctypes.c_uint64(0)
+        _check(self._lib.sh_turbo_create(ctypes.byref(out)), "TransferEngine")
+        self._handle = int(out.value)
+        self._timeout = int(wait_timeout_ms)
+
+    def register_block(self, param_sizes: list[int]) -> int:
+        out = ctypes.c_int32(0)
+        _check(self._lib.sh_turbo_register_block(self._handle, _u64_array(param_sizes), len(param_sizes), ctypes.byref(out)),
+               "register_block")
+        return int(out.value)
+
+    def initialize(self, device: int, window_size: int) -> None:
+        _check(self._lib.sh_turbo_initialize(self._handle, int(device), int(window_size)), "initialize")
+
+    def stage_block(self, block_idx: int, src_ptrs: list[int]) -> None:
+        _check(self._lib.sh_turbo_stage_block(self._handle, int(block_idx), _u64_array(src_ptrs), len(src_ptrs)), "stage_block")
+
+    def set_slot_gpu_ptrs(self, slot_idx: int, ptrs: list[int]) -> None:
+        _check(self._lib.sh_turbo_set_slot_gpu_ptrs(self._handle, int(slot_idx), _u64_array(ptrs), len(ptrs)), "set_slot_gpu_ptrs")
+
+    def step(self, block_idx: int, direction: str) -> None:
+        if direction not in ("forward", "backward"):
+            raise ValueError("direction must be 'forward' or 'backward'")
+        stream = torch.cuda.current_stream().cuda_stream
+        _check(self._lib.sh_turbo_step(self._handle, int(block_idx), 1 if direction == "backward" else 0, stream,
+                                       self._timeout), "step")
+
+    def evict_sync(self, block_idx: int) -> None:
+        stream = torch.cuda.current_stream().cuda_stream
+        _check(self._lib.sh_turbo_evict_sync(self._handle, int(block_idx), stream, self._timeout), "evict_sync")
+
+    def _ptr(self, block_idx: int, param_idx: int, on_gpu: bool) -> int:
+        out = ctypes.c_uint64(0)
+        _check(self._lib.sh_turbo_ptr(self._handle, int(block_idx), int(param_idx), 1 if on_gpu else 0, ctypes.byref(out)), "ptr")
+        return int(out.value)
+
+    def gpu_ptr(self, block_idx: int, param_idx: int) -> int:
+        return self._ptr(block_idx, param_idx, True)
+
+    def cpu_ptr(self, block_idx: int, param_idx: int) -> int:
+        return self._ptr(block_idx, param_idx, False)
+
+    def _state(self, block_idx: int) -> tuple[int, int]:
+        loc, slot = ctypes.c_int32(0), ctypes.c_int32(-1)
+        _check(self._lib.sh_turbo_block_state(self._handle, int(block_idx), ctypes.byref(loc), ctypes.byref(slot)), "block_state")
+        return int(loc.value), int(slot.value)
+
+    def block_slot(self, block_idx: int) -> int | None:
+        slot = self._state(block_idx)[1]
+        return None if slot < 0 else slot
+
+    def block_location(self, block_idx: int) -> str:
+        return _LOCATIONS[self._state(block_idx)[0]]
+
+    def _counts(self) -> tuple[int, int, int]:
+        a, b, c = ctypes.c_int32(0), ctypes.c_int32(0), ctypes.c_int32(0)
+        _check(self._lib.sh_turbo_counts(self._handle, ctypes.byref(a), ctypes.byref(b), ctypes.byref(c)), "counts")
+        return int(a.value), int(b.value), int(c.value)
+
+    def num_blocks(self) -> int:
+        return self._counts()[0]
+
+    def num_gpu_slots(self) -> int:
+        return self._counts()[1]
+
+    def num_free_slots(self) -> int:
+        return self._counts()[2]
+
+    def drain(self) -> None:
+        _check(self._lib.sh_turbo_drain(self._handle, self._timeout), "drain")
+
+    def close(self) -> None:
+        if self._handle:
+            self._lib.sh_turbo_destroy(self._handle)
+            self._handle = 0
+
+    def __del__(self) -> None:
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class TurboConductor:
+    """Block swapping through a window of three GPU slots."""
+
+    WINDOW = 3
+
+    def __init__(self, model: nn.Module, block_pattern: str = r".*\.block\.\d+$", dtype: torch.dtype = torch.bfloat16,
+                 device: int = 0, vram_budget_gb: float = 18.0) -> None:
+        if not is_available():
+            raise RuntimeError("the native transfer engine needs a CUDA device and the built library")
+        self._dtype, self._device_idx = dtype, int(device)
+        self._device = torch.device("cuda", self._device_idx)
+        matcher = re.compile(block_pattern)
+        found = [(name, mod) for name, mod in model.named_modules() if matcher.match(name)]
+        if not found:
+            raise ValueError(f"No blocks matched {block_pattern!r}")
+        self._block_names = [n for n, _ in found]
+        self._block_modules = [m for _, m in found]
+        self._engine: TransferEngine | None = None
+        self._prepared = False
+        self._param_meta: list[list[tuple[str, tuple[int, ...], int]]] = []
+        self._slot_tensors: list[list[torch.Tensor]] = []
+        self._cpu_tensors: list[list[torch.Tensor]] = []
+
+    @property
+    def num_blocks(self) -> int:
+        return len(self._block_modules)
+
+    def prepare(self) -> None:
+        if self._prepared:
+            return
+        engine = TransferEngine()
+        for mod in self._block_modules:
+            meta = [(n, tuple(p.shape), p.numel() * self._dtype.itemsize) for n, p in mod.named_parameters()]
+            engine.register_block([nbytes for _n, _s, nbytes in meta])
+            self._param_meta.append(meta)
+        engine.initialize(self._device_idx, self.WINDOW)
+        for index, mod in enumerate(self._block_modules):
+            staged = [p.data.detach().cpu().to(self._dtype).contiguous() for _n, p in mod.named_parameters()]
+            engine.stage_block(index, [t.data_ptr() for t in staged])
+            views = []
+            for param_idx, (_n, shape, nbytes) in enumerate(self._param_meta[index]):
+                raw = (ctypes.c_char * max(nbytes, 1)).from_address(engine.cpu_ptr(index, param_idx)) if nbytes else None
+                views.append(torch.frombuffer(raw, dtype=self._dtype, count=nbytes // self._dtype.itemsize).reshape(shape)
+                             if nbytes else torch.empty(shape, dtype=self._dtype))
+            self._cpu_tensors.append(views)
+        max_params = max(len(m) for m in self._param_meta)
+        capacity = [max((m[i][2] for m in self._param_meta if i < len(m)), default=0) for i in range(max_params)]
+        for slot in range(engine.num_gpu_slots()):
+            tensors = [torch.empty(nbytes // self._dtype.itemsize, dtype=self._dtype, device=self._device) for nbytes in capacity]
+            engine.set_slot_gpu_ptrs(slot, [t.data_ptr() for t in tensors])
+            self._slot_tensors.append(tensors)
+        for index, mod in enumerate(self._block_modules):
+            for param_idx, (_n, p) in enumerate(mod.named_parameters()):
+                p.data = self._cpu_tensors[index][param_idx]
+        self._engine, self._prepared = engine, True
+        log.info("TurboConductor: ready, %d slots, %d blocks", engine.num_gpu_slots(), len(self._block_modules))
+
+    def before_block(self, block_idx: int, direction: str = "forward") -> None:
+        assert self._engine is not None, "call prepare() first"
+        self._engine.step(block_idx, direction)
+        slot = self._engine.block_slot(block_idx)
+        if slot is None:
+            raise RuntimeError(f"Block {block_idx} has no GPU slot after step()")
+        for param_idx, (_n, p) in enumerate(self._block_modules[block_idx].named_parameters()):
+            shape = self._param_meta[block_idx][param_idx][1]
+            p.data = self._slot_tensors[slot][param_idx][: p_numel(shape)].reshape(shape)
+
+    def after_block(self, block_idx: int) -> None:
+        for param_idx, (_n, p) in enumerate(self._block_modules[block_idx].named_parameters()):
+            p.data = self._cpu_tensors[block_idx][param_idx]
+
+    def evict_all(self) -> None:
+        if self._engine is None:
+            return
+        for index in range(len(self._block_modules)):
+            if self._engine.block_location(index) in ("gpu", "h2d"):
+                self._engine.evict_sync(index)
+        for index in range(len(self._block_modules)):
+            self.after_block(index)
+
+    def shutdown(self) -> None:
+        if self._engine is not None:
+            self._engine.drain()
+        self._slot_tensors.clear()     # parameters already point at host views; drop the GPU window
+        for index in range(len(self._block_modules)):
+            for param_idx, (_n, p) in enumerate(self._block_modules[index].named_parameters()):
+                p.data = self._cpu_tensors[index][param_idx].clone()     # host memory is freed with the engine
+        self._cpu_tensors.clear()
+        if self._engine is not None:
+            self._engine.close()
+            self._engine = None
+
+
+def p_numel(shape: tuple[int, ...]) -> int:
+    n = 1
+    for d in shape:
+        n *= int(d)
+    return n

@@ -60,6 +60,8 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--layout", default="striped", choices=["striped", "owner"],
                     help="multi-GPU: rows of every weight striped over all ranks, or whole blocks round-robin")
     ap.add_argument("--no-fused", action="store_true", help="multi-GPU: copy-engine pull + kernel instead of the fused kernel")
+    ap.add_argument("--no-wraparound", action="store_true",
+                    help="stop the prefetch window at the last block, as the reference does (each step then starts cold)")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--skip-delivery-only", action="store_true")
     ap.add_argument("--unique-weights", action="store_true", help="write every layer's own tensors into the slab file")
@@ -169,7 +171,7 @@ def make_runtime(args, model, fpk: Path, pattern: str):
         vram_high_watermark_mb=int(budget_mb * 0.8), vram_low_watermark_mb=int(budget_mb * 0.6),
         prefetch_window_blocks=args.prefetch_k, eviction_cooldown_steps=0,
         nan_inf_check=False, strict_bf16=False, telemetry_enabled=True, telemetry_interval_steps=0,
-        telemetry_file=os.devnull, packed_image_cache_mb=-1)
+        telemetry_file=os.devnull, packed_image_cache_mb=-1, prefetch_wraparound=not args.no_wraparound)
     rt = sh.StagehandRuntime(model, cfg, block_pattern=pattern, group="dit", dtype=torch.bfloat16,
                              inference_mode=True)
     converted = rt.convert_registry_to_file_backed(str(fpk))
@@ -543,7 +545,8 @@ def compose_line(args, world: int, results: dict, peaks: dict, link_peak: float,
         "warmup": args.warmup, "ms_per_step": v["ms_total"] / K, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": v["desc"]["workload"], "arithmetic": "int8 -> fp32 (subtract, multiply) -> bf16, round to nearest even", "vram_budget_gb": args.vram_budget_gb,
-                   "prefetch_k": args.prefetch_k, "int8_elements_per_forward": v["desc"]["int8_elements"],
+                   "prefetch_k": args.prefetch_k,
+                   "prefetch_wraparound": not args.no_wraparound, "int8_elements_per_forward": v["desc"]["int8_elements"],
                    "l2": "inputs larger than L2 (11.8 GB of INT8 per step); no flush",
                    "value_source": "INT8 images resident in HBM" + ("" if world == 1 else
                                    f", {args.layout} layout over {world} GPUs, " +

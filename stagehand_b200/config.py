@@ -55,6 +55,9 @@ class StagehandConfig:
     device_staging_slabs: int = 0
     # Host threads used to pack an image that is not cached.
     pack_threads: int = 8
+    # Inference only: let the prefetch window run past the last block into the first blocks of the next
+    # pass (the reference's window stops at the last block, so every pass starts with an exposed load).
+    prefetch_wraparound: bool = False
     # Where the block slabs in VRAM come from: "torch" (caching allocator) or "vmm" (the C++ virtual-memory
     # slab allocator: parked slabs can be unmapped under `vmm_ceiling_mb` without fragmenting anything).
     device_pool_backend: str = "torch"

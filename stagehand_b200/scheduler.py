@@ -434,7 +434,14 @@ class StagehandScheduler:
 
     def _prefetch_ahead(self) -> None:
         states = _ResidencyStates(self._residency, self._block_ids)
-        for idx in self._policy.blocks_to_prefetch(self._cursor - 1, self._total_blocks, states):
+        wanted = list(self._policy.blocks_to_prefetch(self._cursor - 1, self._total_blocks, states))
+        if (getattr(self._config, "prefetch_wraparound", False) and self._inference_mode and not self._backward_phase
+                and self._total_blocks > 0):
+            # Inference passes start over at block 0: near the end of a pass the window runs on into the
+            # first blocks of the next one, so the link does not idle between passes.
+            overflow = self._cursor + self._policy.prefetch_window - self._total_blocks
+            wanted += [i for i in range(min(max(overflow, 0), self._total_blocks)) if i not in wanted]
+        for idx in wanted:
             if idx >= self._total_blocks:
                 break
             block_id = self._ordered_blocks[idx].block_id

@@ -229,3 +229,22 @@ def test_virtual_memory_slab_backend(tmp_path: Path) -> None:
     assert rt._budget.vram_used_mb() >= 24                    # the mapped slabs count although torch did not allocate them
     rt.shutdown()
     assert all(b.qkv.weight.numel() == 0 for b in model.blocks)   # nothing points into unmapped memory
+
+
+def test_prefetch_window_wraps_into_the_next_pass(tmp_path: Path) -> None:
+    """With prefetch_wraparound the first blocks of the next pass are already in flight when a pass ends."""
+    model, rt, x = _build("cfg1", tmp_path, vram_high_watermark_mb=60, vram_low_watermark_mb=30,
+                          prefetch_window_blocks=2, prefetch_wraparound=True)
+    outs = []
+    for step in range(3):
+        rt.begin_step(step)
+        with torch.inference_mode(), rt.managed_forward():
+            outs.append(model(x))
+        rt.end_step()
+        first = rt._residency.get_state("blocks.0")
+        assert first in (sh.BlockState.PREFETCHING, sh.BlockState.GPU_READY)
+    torch.cuda.synchronize()
+    assert all(_rel_l2(y, "cfg1") <= 1e-2 for y in outs) and torch.equal(outs[0], outs[2])
+    last = rt.telemetry.last()
+    assert last.dequant_launches == 4 and last.prefetch_misses <= 4
+    rt.shutdown()

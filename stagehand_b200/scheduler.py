@@ -432,11 +432,14 @@ class StagehandScheduler:
 
     # ── prefetch ─────────────────────────────────────────────────────
 
+    def _wraparound_active(self) -> bool:
+        return bool(self._config.prefetch_wraparound and self._inference_mode and not self._backward_phase
+                    and self._total_blocks > 0)
+
     def _prefetch_ahead(self) -> None:
         states = _ResidencyStates(self._residency, self._block_ids)
         wanted = list(self._policy.blocks_to_prefetch(self._cursor - 1, self._total_blocks, states))
-        if (getattr(self._config, "prefetch_wraparound", False) and self._inference_mode and not self._backward_phase
-                and self._total_blocks > 0):
+        if self._wraparound_active():
             # Inference passes start over at block 0: near the end of a pass the window runs on into the
             # first blocks of the next one, so the link does not idle between passes.
             overflow = self._cursor + self._policy.prefetch_window - self._total_blocks
@@ -793,10 +796,11 @@ class StagehandScheduler:
         cooldown = 0 if ignore_cooldown else self._policy.eviction_cooldown_steps
         candidates = self._residency.eviction_candidates(self._current_step, cooldown)
         window_start = max(self._cursor - 1, 0)
+        wrap = self._wraparound_active()
         protected = {
-            self._ordered_blocks[i].block_id
+            self._ordered_blocks[i % self._total_blocks].block_id
             for i in range(window_start + 1, window_start + 1 + self._policy.prefetch_window)
-            if i < self._total_blocks
+            if i < self._total_blocks or wrap
         }
         ranked = []
         for block_id, _res in candidates:

@@ -58,6 +58,9 @@ class StagehandConfig:
     # Inference only: let the prefetch window run past the last block into the first blocks of the next
     # pass (the reference's window stops at the last block, so every pass starts with an exposed load).
     prefetch_wraparound: bool = False
+    # Training: during the backward pass prefetch the blocks *below* the one being differentiated (the
+    # reference's window only looks forward, so its backward pass loads every block on demand).
+    backward_prefetch: bool = False
     # Where the block slabs in VRAM come from: "torch" (caching allocator) or "vmm" (the C++ virtual-memory
     # slab allocator: parked slabs can be unmapped under `vmm_ceiling_mb` without fragmenting anything).
     device_pool_backend: str = "torch"

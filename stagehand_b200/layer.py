@@ -163,7 +163,8 @@ class LayerRuntime:
             pre = self._scheduled_pre_hook(layer_id) if traced else self._trace_pre_hook(layer_id)
             self._hook_handles.append(module.register_forward_pre_hook(pre))
             self._hook_handles.append(module.register_forward_hook(
-                lambda _m, _a, out, lid=layer_id: self._scheduler.after_block(lid, _first_tensor(out))))
+                lambda _m, _a, out, lid=layer_id: self._scheduler.after_block(lid, _first_tensor(out)),
+                always_call=True))         # a forward abandoned by an exception still drops its reference
         if not self._inference_mode:
             for layer_id in (reversed(order) if traced else order):
                 module = self._layer_map.get(layer_id)

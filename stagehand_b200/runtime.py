@@ -141,10 +141,14 @@ class StagehandRuntime:
                     self._scheduler.before_block(bid)
 
                 def post(_m, _args, output, bid=bid):
+                    if output is None and self._residency.get_entry(bid).refcount == 0:
+                        return      # the forward failed before the block was taken: nothing to drop
                     self._scheduler.after_block(bid, _first_tensor(output))
 
                 handles.append(module.register_forward_pre_hook(pre))
-                handles.append(module.register_forward_hook(post))
+                # always_call: activation checkpointing may abandon a recomputed forward half-way (it stops
+                # as soon as the tensors it needs exist); the block's reference must be dropped all the same.
+                handles.append(module.register_forward_hook(post, always_call=True))
         return handles
 
     @contextmanager

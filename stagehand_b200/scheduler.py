@@ -170,6 +170,7 @@ class StagehandScheduler:
 
         self._current_step = 0
         self._cursor = 0
+        self._current_index = -1
         self._backward_phase = False
         self._defer_backward_eviction = False
 
@@ -209,6 +210,7 @@ class StagehandScheduler:
         self._total_blocks = len(self._ordered_blocks)
         self._order_to_id = {e.exec_order: e.block_id for e in self._ordered_blocks}
         self._block_ids = [e.block_id for e in self._ordered_blocks]
+        self._index_of = {bid: i for i, bid in enumerate(self._block_ids)}
         self._view_cache: dict[tuple[str, int], list[tuple[Any, str, torch.Tensor]]] = {}
         if getattr(self, "_image_plans", None):
             self._image_plans.clear()
@@ -216,6 +218,7 @@ class StagehandScheduler:
     def begin_step(self, step: int) -> None:
         self._current_step = step
         self._cursor = 0
+        self._current_index = -1
         self._backward_phase = False
         self._telemetry.begin_step(step)
 
@@ -392,6 +395,7 @@ class StagehandScheduler:
         self._residency.increment_ref(block_id)
         self._residency.get_entry(block_id).last_used_step = self._current_step
         self._cursor += 1
+        self._current_index = self._index_of.get(block_id, -1)
 
         if self._budget.above_high_watermark():
             self._run_eviction(ignore_cooldown=True)
@@ -436,9 +440,26 @@ class StagehandScheduler:
         return bool(self._config.prefetch_wraparound and self._inference_mode and not self._backward_phase
                     and self._total_blocks > 0)
 
+    def _backward_window(self) -> list[int] | None:
+        """Indices the backward pass reaches next (descending), or None when backward prefetch is off.
+
+        The reference's window only looks forward (``scheduler.py:854-883``: the cursor keeps
+        counting up through the backward pass, so nothing is ever ahead of it and every block
+        the backward pass needs is loaded on demand).  With ``backward_prefetch`` the window
+        runs downwards from the block being differentiated.
+        """
+        if not (self._backward_phase and self._config.backward_prefetch) or self._current_index < 0:
+            return None
+        cur = self._current_index
+        return [i for i in range(cur - 1, cur - 1 - self._policy.prefetch_window, -1) if i >= 0]
+
     def _prefetch_ahead(self) -> None:
         states = _ResidencyStates(self._residency, self._block_ids)
-        wanted = list(self._policy.blocks_to_prefetch(self._cursor - 1, self._total_blocks, states))
+        backward = self._backward_window()
+        if backward is not None:
+            wanted = backward
+        else:
+            wanted = list(self._policy.blocks_to_prefetch(self._cursor - 1, self._total_blocks, states))
         if self._wraparound_active():
             # Inference passes start over at block 0: near the end of a pass the window runs on into the
             # first blocks of the next one, so the link does not idle between passes.
@@ -797,16 +818,27 @@ class StagehandScheduler:
         candidates = self._residency.eviction_candidates(self._current_step, cooldown)
         window_start = max(self._cursor - 1, 0)
         wrap = self._wraparound_active()
-        protected = {
-            self._ordered_blocks[i % self._total_blocks].block_id
-            for i in range(window_start + 1, window_start + 1 + self._policy.prefetch_window)
-            if i < self._total_blocks or wrap
-        }
+        backward = self._backward_window()
+        if backward is not None:
+            protected = {self._block_ids[i] for i in backward}
+        else:
+            protected = {
+                self._ordered_blocks[i % self._total_blocks].block_id
+                for i in range(window_start + 1, window_start + 1 + self._policy.prefetch_window)
+                if i < self._total_blocks or wrap
+            }
         ranked = []
         for block_id, _res in candidates:
             if block_id in protected:
                 continue
             entry = self._registry.get(block_id)
+            if backward is not None:
+                # Going down: blocks below the current one are needed soon; those at or above it are done
+                # until the next forward pass reaches them again.
+                order, cur = self._index_of[block_id], self._current_index
+                distance = cur - order if order < cur else cur + 1 + order
+                ranked.append((float(distance * entry.size_bytes), block_id))
+                continue
             ranked.append((self._policy.score_for_eviction(block_id, self._cursor, entry.exec_order,
                                                            self._total_blocks, entry.size_bytes), block_id))
         ranked.sort(reverse=True)

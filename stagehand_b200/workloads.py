@@ -33,6 +33,9 @@ __all__ = [
     "TinyBlockModel",
     "FluxShapedDiT",
     "MistralShapedEncoder",
+    "LoraLinear",
+    "VideoShapedDiT",
+    "write_sharded_safetensors",
     "synth_squareq_layer",
     "write_squareq_fpk",
     "BLOCK_PATTERNS",
@@ -256,10 +259,169 @@ class MistralShapedEncoder(nn.Module):
         return x
 
 
+# ── config 3: bf16 video-DiT-shaped blocks with rank-r adapters (forward + backward) ──────────
+
+
+class LoraLinear(nn.Module):
+    """A frozen bias-free projection (``base.weight``, streamed from a file) plus a trainable rank-r adapter.
+
+    ``lora_a`` / ``lora_b`` require gradients, so the registry keeps them module-owned
+    (reference ``src/stagehand/registry.py:648-650``): they are staged fresh at every load
+    and their gradients are kept at eviction.
+    """
+
+    def __init__(self, in_features: int, out_features: int, rank: int, device=None, dtype=None) -> None:
+        super().__init__()
+        self.base = nn.Linear(in_features, out_features, bias=False, device=device, dtype=dtype)
+        self.lora_a = nn.Parameter(torch.empty(rank, in_features, device=device, dtype=dtype))
+        self.lora_b = nn.Parameter(torch.empty(out_features, rank, device=device, dtype=dtype))
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.base(x) + F.linear(F.linear(x, self.lora_a), self.lora_b)
+
+
+class _VideoDiTBlock(nn.Module):
+    """Self-attention, cross-attention to a text context and a GELU feed-forward, all pre-norm."""
+
+    def __init__(self, hidden: int, heads: int, ffn: int, rank: int, device=None, dtype=None) -> None:
+        super().__init__()
+        kw = dict(device=device, dtype=dtype)
+        self.heads = heads
+        self.norm1 = nn.RMSNorm(hidden, **kw)
+        self.attn_q, self.attn_k, self.attn_v, self.attn_o = (LoraLinear(hidden, hidden, rank, **kw) for _ in range(4))
+        self.norm2 = nn.RMSNorm(hidden, **kw)
+        self.cross_q, self.cross_k, self.cross_v, self.cross_o = (LoraLinear(hidden, hidden, rank, **kw) for _ in range(4))
+        self.norm3 = nn.RMSNorm(hidden, **kw)
+        self.fc1 = nn.Linear(hidden, ffn, bias=False, **kw)
+        self.fc2 = nn.Linear(ffn, hidden, bias=False, **kw)
+
+    def forward(self, x: torch.Tensor, context: torch.Tensor) -> torch.Tensor:
+        n = self.heads
+        h = self.norm1(x)
+        x = x + self.attn_o(_sdpa(_heads(self.attn_q(h), n), _heads(self.attn_k(h), n), _heads(self.attn_v(h), n)))
+        h = self.norm2(x)
+        x = x + self.cross_o(_sdpa(_heads(self.cross_q(h), n), _heads(self.cross_k(context), n),
+                                   _heads(self.cross_v(context), n)))
+        return x + self.fc2(F.gelu(self.fc1(self.norm3(x))))
+
+
+class VideoShapedDiT(nn.Module):
+    """48 blocks, hidden 4096, 32 heads, FFN 16384, rank-32 adapters on the eight attention projections.
+
+    With these dimensions a block holds 8 x 4096^2 + 2 x 4096 x 16384 = 268.4 M frozen weights
+    (12.9 G in 48 blocks, 25.8 GB in bf16) and 2.1 M trainable adapter weights.  With
+    ``checkpoint_blocks`` every block runs under activation checkpointing, the way the
+    reference's training case study runs (its blocks are recomputed during backward).
+    """
+
+    def __init__(self, n_blocks: int = 48, hidden: int = 4096, heads: int = 32, ffn: int = 16384, rank: int = 32,
+                 checkpoint_blocks: bool = True, device=None, dtype=None) -> None:
+        super().__init__()
+        self.checkpoint_blocks = checkpoint_blocks
+        self.blocks = nn.ModuleList(_VideoDiTBlock(hidden, heads, ffn, rank, device, dtype) for _ in range(n_blocks))
+
+    def init_adapters(self, seed: int = 0, std: float = 0.02) -> None:
+        """Real storage and seeded values for the adapters (also when the model was built on ``meta``)."""
+        g = torch.Generator().manual_seed(seed)
+        for module in self.modules():
+            if isinstance(module, LoraLinear):
+                for name in ("lora_a", "lora_b"):
+                    old = getattr(module, name)
+                    value = (torch.randn(old.shape, generator=g) * std).to(old.dtype)
+                    setattr(module, name, nn.Parameter(value, requires_grad=True))
+
+    def forward(self, x: torch.Tensor, context: torch.Tensor) -> torch.Tensor:
+        from torch.utils.checkpoint import checkpoint
+
+        for block in self.blocks:
+            if self.checkpoint_blocks and torch.is_grad_enabled():
+                x = checkpoint(block, x, context, use_reentrant=False)
+            else:
+                x = block(x, context)
+        return x
+
+
+_SAFETENSORS_DTYPES = {torch.bfloat16: "BF16", torch.float16: "F16", torch.float32: "F32"}
+
+
+def _write_safetensors(tensors: dict[str, torch.Tensor], path: Path) -> None:
+    """One safetensors file: u64 header length, JSON header, then the tensors' bytes in header order.
+
+    Written directly (not through ``safetensors.torch.save_file``) so that several names may
+    carry the same in-memory tensor: each still gets its own region of the file.
+    """
+    import json
+    import struct
+
+    header: dict[str, dict] = {}
+    cursor = 0
+    for name, t in tensors.items():
+        nbytes = t.numel() * t.element_size()
+        header[name] = {"dtype": _SAFETENSORS_DTYPES[t.dtype], "shape": list(t.shape),
+                        "data_offsets": [cursor, cursor + nbytes]}
+        cursor += nbytes
+    raw = json.dumps(header, separators=(",", ":")).encode("utf-8")
+    raw += b" " * (-len(raw) % 8)
+    with open(path, "wb") as fh:
+        fh.write(struct.pack("<Q", len(raw)))
+        fh.write(raw)
+        for t in tensors.values():
+            fh.write(memoryview(t.contiguous().view(torch.uint8).numpy()))
+
+
+def write_sharded_safetensors(model: nn.Module, out_dir: str | Path, blocks_per_shard: int = 4, seed: int = 0,
+                              std: float = 0.02, dtype: torch.dtype = torch.bfloat16,
+                              share_values: bool = True) -> dict[str, int]:
+    """Frozen (``requires_grad == False``) 2-D parameters of *model* as a sharded safetensors checkpoint.
+
+    Values are ``randn * std``.  With *share_values* the blocks all get the value set of one block
+    (tensors of one shape share one draw), which keeps set-up short; every tensor still has its own
+    region in the files.  Writes ``model.safetensors.index.json`` with the ``weight_map`` the sharded
+    conversion reads (reference ``src/stagehand/registry.py:560-702``).  Returns ``{"tensors", "bytes", "shards"}``.
+    """
+    import json
+
+    out_dir = Path(out_dir)
+    out_dir.mkdir(parents=True, exist_ok=True)
+    g = torch.Generator().manual_seed(seed)
+    by_shape: dict[tuple[int, ...], torch.Tensor] = {}
+
+    def value(shape: tuple[int, ...]) -> torch.Tensor:
+        if share_values and shape in by_shape:
+            return by_shape[shape]
+        t = (torch.randn(shape, generator=g) * std).to(dtype)
+        by_shape[shape] = t
+        return t
+
+    groups: dict[str, list[tuple[str, tuple[int, ...]]]] = {}
+    for name, param in model.named_parameters():
+        if param.requires_grad or param.dim() < 2:
+            continue
+        m = re.match(r"^(.*?\.\d+)\.", name)
+        groups.setdefault(m.group(1) if m else "", []).append((name, tuple(param.shape)))
+    keys = list(groups)
+    weight_map: dict[str, str] = {}
+    total = tensors = 0
+    n_shards = (len(keys) + blocks_per_shard - 1) // blocks_per_shard
+    for shard in range(n_shards):
+        fname = f"model-{shard + 1:05d}-of-{n_shards:05d}.safetensors"
+        payload = {}
+        for key in keys[shard * blocks_per_shard:(shard + 1) * blocks_per_shard]:
+            for name, shape in groups[key]:
+                payload[name] = value(shape)
+                weight_map[name] = fname
+                total += payload[name].numel() * payload[name].element_size()
+                tensors += 1
+        _write_safetensors(payload, out_dir / fname)
+    (out_dir / "model.safetensors.index.json").write_text(json.dumps({"weight_map": weight_map}))
+    return {"tensors": tensors, "bytes": total, "shards": n_shards}
+
+
 BLOCK_PATTERNS = {
     "tiny": r"^blocks\.\d+$",
     "flux": r"^(double_blocks|single_blocks)\.\d+$",
     "mistral": r"^layers\.\d+$",
+    "video": r"^blocks\.\d+$",
 }
 
 

@@ -145,6 +145,75 @@ def test_training_step_with_trainable_adapters(tmp_path: Path) -> None:
     rt.shutdown()
 
 
+def _video_pair(tmp_path: Path, dtype: torch.dtype = torch.float32):
+    """A small adapter-carrying DiT streamed from a sharded checkpoint, and a resident twin with the same values."""
+    from safetensors import safe_open
+
+    from stagehand_b200.workloads import VideoShapedDiT, write_sharded_safetensors
+
+    kw = dict(n_blocks=4, hidden=64, heads=4, ffn=128, rank=4, dtype=dtype)
+    model = VideoShapedDiT(**kw)
+    model.init_adapters(seed=5, std=0.05)
+    for name, p in model.named_parameters():
+        p.requires_grad_("lora" in name)
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            if p.dim() == 1:
+                p.fill_(1.0)
+    info = write_sharded_safetensors(model, tmp_path, blocks_per_shard=3, seed=1, std=0.1, dtype=dtype,
+                                     share_values=False)
+    assert info["shards"] == 2 and info["tensors"] == 4 * 10
+    twin = VideoShapedDiT(**kw)
+    state = {k: v.detach().clone() for k, v in model.state_dict().items()}
+    for shard in sorted(tmp_path.glob("*.safetensors")):
+        with safe_open(str(shard), framework="pt") as fh:
+            for key in fh.keys():
+                state[key] = fh.get_tensor(key)
+    twin.load_state_dict(state)
+    for name, p in twin.named_parameters():
+        p.requires_grad_("lora" in name)
+    return model, twin
+
+
+@pytest.mark.parametrize("tight,backward_prefetch", [(False, False), (True, False), (True, True)])
+def test_checkpointed_blocks_train_under_managed_hooks(tight: bool, backward_prefetch: bool, tmp_path: Path) -> None:
+    """Activation checkpointing recomputes each block during backward: the hooks fire again and find it loaded.
+
+    The recomputed forward is abandoned as soon as the tensors backward needs exist, so its post-forward hook
+    only runs because it is registered to run always; every block's reference count is back at zero after a step.
+    """
+    model, twin = _video_pair(tmp_path)
+    extra = dict(vram_high_watermark_mb=1, vram_low_watermark_mb=0, eviction_cooldown_steps=0) if tight else {}
+    cfg = sh.StagehandConfig(pinned_pool_mb=8, pinned_slab_mb=1, telemetry_enabled=True, nan_inf_check=False,
+                             telemetry_file=str(tmp_path / "t.jsonl"), prefetch_window_blocks=2,
+                             backward_prefetch=backward_prefetch, **extra)
+    rt = sh.StagehandRuntime(model, cfg, block_pattern=r"^blocks\.\d+$", dtype=torch.float32, inference_mode=False)
+    assert rt.convert_registry_to_file_backed_sharded(str(tmp_path)) == 4 * 10
+    device = "cuda" if torch.cuda.is_available() else "cpu"
+    g = torch.Generator().manual_seed(4)
+    x, ctx = torch.randn(2, 12, 64, generator=g), torch.randn(2, 5, 64, generator=g)
+    for step in range(2):
+        rt.begin_step(step)
+        with rt.managed_forward(), rt.managed_backward():
+            loss = model(x.to(device).requires_grad_(True), ctx.to(device)).pow(2).mean()
+            loss.backward()
+        rt.end_step()
+        twin.zero_grad()
+        ref_loss = twin(x.clone().requires_grad_(True), ctx).pow(2).mean()
+        ref_loss.backward()
+        assert abs(float(loss.detach()) - float(ref_loss.detach())) < 1e-4 * max(1.0, abs(float(ref_loss.detach())))
+        for (name, got), (_n, ref) in zip(model.named_parameters(), twin.named_parameters()):
+            if "lora" in name:
+                assert got.grad is not None, name
+                assert torch.allclose(got.grad.cpu(), ref.grad, atol=1e-5, rtol=1e-3), name
+        model.zero_grad()
+        assert all(rt._residency.get_entry(e.block_id).refcount == 0 for e in rt._registry.blocks_in_order())
+        if tight and device == "cuda":
+            last = rt.telemetry.last()
+            assert last.evictions >= 4                      # nothing stays pinned in VRAM by a leaked reference
+    rt.shutdown()
+
+
 # ── the same scenarios on a GPU: safetensors-backed blocks go through the packed-image path ──────────
 
 
@@ -164,3 +233,61 @@ def test_gpu_file_dtype_cast_and_training(tmp_path: Path) -> None:
     (tmp_path / "b").mkdir()
     test_file_dtype_is_cast_to_the_runtime_dtype(tmp_path / "a")
     test_training_step_with_trainable_adapters(tmp_path / "b")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("tight,backward_prefetch", [(False, False), (True, False), (True, True)])
+def test_gpu_checkpointed_blocks_train_under_managed_hooks(tight: bool, backward_prefetch: bool, tmp_path: Path) -> None:
+    test_checkpointed_blocks_train_under_managed_hooks(tight, backward_prefetch, tmp_path)
+
+
+@pytest.mark.gpu
+def test_gpu_backward_pass_prefetches_downwards(tmp_path: Path) -> None:
+    """With ``backward_prefetch`` block i-1 is already in flight when block i's gradient arrives."""
+    import gc
+
+    from stagehand_b200.workloads import VideoShapedDiT, write_sharded_safetensors
+
+    demand: dict[bool, int] = {}
+    grads: dict[bool, list[torch.Tensor]] = {}
+    for enabled in (False, True):
+        torch.manual_seed(0)
+        model = VideoShapedDiT(n_blocks=6, hidden=512, heads=8, ffn=2048, rank=4, dtype=torch.float32)
+        model.init_adapters(seed=5, std=0.05)
+        for name, p in model.named_parameters():
+            p.requires_grad_("lora" in name)
+        ckpt = tmp_path / f"ckpt{int(enabled)}"
+        write_sharded_safetensors(model, ckpt, blocks_per_shard=4, seed=1, std=0.05, dtype=torch.float32)
+        gc.collect()
+        base_mb = int(torch.cuda.memory_allocated() >> 20)
+        # a block is 16.8 MB: room for about three of the six
+        cfg = sh.StagehandConfig(pinned_pool_mb=64, pinned_slab_mb=32, telemetry_enabled=False, nan_inf_check=False,
+                                 prefetch_window_blocks=1, eviction_cooldown_steps=0, backward_prefetch=enabled,
+                                 vram_high_watermark_mb=base_mb + 75, vram_low_watermark_mb=base_mb + 40)
+        rt = sh.StagehandRuntime(model, cfg, block_pattern=r"^blocks\.\d+$", dtype=torch.float32, inference_mode=False)
+        rt.convert_registry_to_file_backed_sharded(str(ckpt))
+        sched = rt._scheduler
+        inner = sched._load_block_to_gpu
+        count = [0]
+
+        def counted(block_id, speculative=False, _inner=inner, _sched=sched, _count=count):
+            if not speculative and _sched._backward_phase:
+                _count[0] += 1
+            return _inner(block_id, speculative=speculative)
+
+        sched._load_block_to_gpu = counted
+        g = torch.Generator().manual_seed(4)
+        x, ctx = torch.randn(1, 64, 512, generator=g).cuda(), torch.randn(1, 8, 512, generator=g).cuda()
+        for step in range(2):
+            rt.begin_step(step)
+            with rt.managed_forward(), rt.managed_backward():
+                model(x.clone().requires_grad_(True), ctx).pow(2).mean().backward()
+            rt.end_step()
+        demand[enabled] = count[0]
+        grads[enabled] = [p.grad.detach().cpu().clone() for n, p in model.named_parameters() if "lora" in n]
+        rt.shutdown()
+        del model, rt
+    assert demand[False] >= 4                 # the reference's window never looks down: loads on demand
+    assert demand[True] <= demand[False] // 2
+    for a, b in zip(grads[False], grads[True]):
+        assert torch.equal(a, b)              # the same arithmetic either way

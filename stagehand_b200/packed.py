@@ -136,9 +136,13 @@ class PackedBlockImage:
         A parameter whose element count matches is read from the module (and
         remembered in *cache* the first time); one emptied by eviction comes from
         *cache*; anything else becomes a zero-fill descriptor.  With *persistent* (the buffer is this
-        block's own long-lived image, never lent to another block) a slot whose source tensor is the
-        same object and has not been modified since it was staged is left as it is.  Returns whether
-        anything in the dynamic section (bytes or descriptor kinds) changed.
+        block's own long-lived image, never lent to another block, and nothing trains the parameters:
+        the scheduler passes it in inference mode only) a slot whose source is the same memory and
+        whose parameter has not been written through since it was staged is left as it is.  The test
+        is the parameter's own version counter, so a write through a ``.data`` alias is not seen;
+        a training runtime therefore restages every module-owned parameter at every load, as the
+        reference does.  Returns whether anything in the dynamic section (bytes or descriptor kinds)
+        changed.
         """
         if not self.dynamic_rows:
             return False
@@ -146,9 +150,11 @@ class PackedBlockImage:
         for row in self.dynamic_rows:
             desc = self.descs[row.desc_index]
             source: torch.Tensor | None = None
+            version_of: torch.Tensor | None = None
             param = _find_param(module, row.name)
             if param is not None and param.data.numel() == row.numel:
                 source = param.data
+                version_of = param          # ``param.data`` is a fresh alias whose counter always reads 0
                 if cache is not None and row.name not in cache:
                     cache[row.name] = param.data.detach().cpu()
             elif cache is not None and row.name in cache:
@@ -162,8 +168,9 @@ class PackedBlockImage:
                 continue
             self.last_source[row.name] = source.data_ptr()
             # inference tensors carry no version counter: they are always restaged
-            stamp = None if source.is_inference() else (
-                buffer.data_ptr(), source.data_ptr(), source._version, source.dtype, base_offset)
+            counted = version_of if version_of is not None else source
+            stamp = None if (source.is_inference() or counted.is_inference()) else (
+                buffer.data_ptr(), source.data_ptr(), counted._version, source.dtype, base_offset)
             if persistent and stamp is not None and row.staged_from == stamp and desc.kind != SH_KIND_ZERO:
                 continue          # same tensor, not modified since it was last staged: the slot is current
             changed = True

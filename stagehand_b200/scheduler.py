@@ -629,7 +629,7 @@ class StagehandScheduler:
         if plan.dynamic_rows:
             if image.last_copy is not None and not image.last_copy.done():
                 image.last_copy.wait(60_000)   # the previous DMA of this image still reads the dynamic section
-            plan.refresh_dynamic(image.buffer, module, cache, persistent=slab is None)
+            plan.refresh_dynamic(image.buffer, module, cache, persistent=slab is None and self._inference_mode)
         return image, slab
 
     def _load_squareq_block(self, block_id: str, entry: "BlockEntry", res: "ResidencyEntry", state: BlockState) -> None:
@@ -670,7 +670,7 @@ class StagehandScheduler:
         if image.last_copy is not None and not image.last_copy.done():
             image.last_copy.wait(60_000)
         if plan.refresh_dynamic(image.buffer, entry.module_ref(), self._module_param_caches.setdefault(entry.block_id, {}),
-                                base_offset=plan.static_bytes, persistent=True):
+                                base_offset=plan.static_bytes, persistent=self._inference_mode):
             image.dirty = True
         return image, None
 

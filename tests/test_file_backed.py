@@ -192,7 +192,7 @@ def test_checkpointed_blocks_train_under_managed_hooks(tight: bool, backward_pre
     device = "cuda" if torch.cuda.is_available() else "cpu"
     g = torch.Generator().manual_seed(4)
     x, ctx = torch.randn(2, 12, 64, generator=g), torch.randn(2, 5, 64, generator=g)
-    for step in range(2):
+    for step in range(4):
         rt.begin_step(step)
         with rt.managed_forward(), rt.managed_backward():
             loss = model(x.to(device).requires_grad_(True), ctx.to(device)).pow(2).mean()
@@ -206,6 +206,16 @@ def test_checkpointed_blocks_train_under_managed_hooks(tight: bool, backward_pre
             if "lora" in name:
                 assert got.grad is not None, name
                 assert torch.allclose(got.grad.cpu(), ref.grad, atol=1e-5, rtol=1e-3), name
+        # an optimiser step on both; the streamed model must stage the updated adapters at its next load
+        # (alternating the two usual spellings: in place on the parameter, in place through ``.data``)
+        with torch.no_grad():
+            for (name, got), (_n, ref) in zip(model.named_parameters(), twin.named_parameters()):
+                if "lora" in name:
+                    if step % 2 == 0:
+                        got.add_(got.grad.to(got.device), alpha=-0.5)
+                    else:
+                        got.data.add_(got.grad.to(got.device), alpha=-0.5)
+                    ref.add_(ref.grad, alpha=-0.5)
         model.zero_grad()
         assert all(rt._residency.get_entry(e.block_id).refcount == 0 for e in rt._registry.blocks_in_order())
         if tight and device == "cuda":

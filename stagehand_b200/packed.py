@@ -33,6 +33,8 @@ from stagehand_b200 import _native
 from stagehand_b200._native import (SH_DT_BF16, SH_DT_F16, SH_DT_F32, SH_KIND_CAST_F32, SH_KIND_COPY,
                                     SH_KIND_DEQUANT_I8, SH_KIND_ZERO, ShParamDesc)
 
+_COMPARE_BYTES = 64 * 1024      # module-owned parameters up to this size are compared, larger ones version-stamped
+
 __all__ = ["PackedBlockImage", "plan_block_image", "plan_file_image", "runtime_dtype_code", "ALIGN_MATRIX",
            "ALIGN_VECTOR"]
 
@@ -139,8 +141,9 @@ class PackedBlockImage:
         block's own long-lived image, never lent to another block, and nothing trains the parameters:
         the scheduler passes it in inference mode only) a slot whose source is the same memory and
         whose parameter has not been written through since it was staged is left as it is.  The test
-        is the parameter's own version counter, so a write through a ``.data`` alias is not seen;
-        a training runtime therefore restages every module-owned parameter at every load, as the
+        is the parameter's own version counter, so a write through a ``.data`` alias is not seen:
+        slots of up to 64 KiB (norm weights, biases) are therefore compared byte for byte instead,
+        and a training runtime restages every module-owned parameter at every load, as the
         reference does.  Returns whether anything in the dynamic section (bytes or descriptor kinds)
         changed.
         """
@@ -171,9 +174,11 @@ class PackedBlockImage:
             counted = version_of if version_of is not None else source
             stamp = None if (source.is_inference() or counted.is_inference()) else (
                 buffer.data_ptr(), source.data_ptr(), counted._version, source.dtype, base_offset)
-            if persistent and stamp is not None and row.staged_from == stamp and desc.kind != SH_KIND_ZERO:
+            small = row.numel * source.element_size() <= _COMPARE_BYTES and source.device.type == "cpu"
+            if (persistent and not small and stamp is not None and row.staged_from == stamp
+                    and desc.kind != SH_KIND_ZERO):
                 continue          # same tensor, not modified since it was last staged: the slot is current
-            changed = True
+            was_staged = row.staged_from == stamp and stamp is not None and desc.kind != SH_KIND_ZERO
             row.staged_from = stamp
             flat = source.detach().reshape(-1)
             if flat.device.type != "cpu":
@@ -193,7 +198,11 @@ class PackedBlockImage:
                     desc.kind, desc.cols = SH_KIND_COPY, row.numel * self.runtime_dtype.itemsize
             nbytes = flat.numel() * flat.element_size()
             at = row.offset - base_offset   # base_offset = static_bytes when *buffer* holds the dynamic section only
-            buffer[at : at + nbytes].view(flat.dtype).copy_(flat)
+            slot = buffer[at : at + nbytes].view(flat.dtype)
+            if persistent and small and was_staged and torch.equal(slot.view(torch.uint8), flat.view(torch.uint8)):
+                continue          # a small slot is compared byte for byte: exact whatever way it was written
+            changed = True
+            slot.copy_(flat)
         return changed
 
     # ── descriptor views ─────────────────────────────────────────────

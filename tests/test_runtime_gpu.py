@@ -252,3 +252,26 @@ def test_prefetch_window_wraps_into_the_next_pass(tmp_path: Path) -> None:
     last = rt.telemetry.last()
     assert last.dequant_launches >= 3 and last.evictions >= 1     # the model does not fit: blocks are reloaded
     rt.shutdown()
+
+
+@pytest.mark.parametrize("cache_mb", [-1, 0])
+def test_module_owned_parameter_edits_reach_the_next_load(cache_mb: int, tmp_path: Path) -> None:
+    """A norm weight changed between steps -- even in place through ``.data`` -- is what the next load stages."""
+    model, rt, x = _build("cfg1", tmp_path, vram_high_watermark_mb=2, vram_low_watermark_mb=1,
+                          packed_image_cache_mb=cache_mb, prefetch_window_blocks=2)
+    seen: list[torch.Tensor] = []
+    model.blocks[1].register_forward_hook(lambda m, a, o: seen.append(m.norm1.weight.detach().float().cpu().clone()))
+    edits = [lambda p: None, lambda p: p.data.mul_(2.0), lambda p: p.data.add_(1.0),
+             lambda p: setattr(p, "data", p.data * 0.5)]
+    expect = torch.ones(1024)
+    for step, edit in enumerate(edits):
+        param = model.blocks[1].norm1.weight
+        edit(param)
+        expect = [expect, expect * 2.0, expect + 1.0, expect * 0.5][step] if step else expect
+        rt.begin_step(step)
+        with torch.inference_mode(), rt.managed_forward():
+            model(x)
+        rt.end_step()
+        torch.cuda.synchronize()
+        assert torch.equal(seen[-1], expect.to(torch.bfloat16).float()), step
+    rt.shutdown()

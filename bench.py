@@ -53,7 +53,7 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="flux", choices=["flux", "flux_small", "kernel_sweep", "video_train"])
+    ap.add_argument("--workload", default="flux", choices=["flux", "flux_small", "flux_mistral", "kernel_sweep", "video_train"])
     ap.add_argument("--blocks", type=int, default=0, help="video_train: number of blocks (default 48)")
     ap.add_argument("--tokens", type=int, default=6144, help="video_train: video tokens per step")
     ap.add_argument("--shapes", default="", help="kernel_sweep: comma-separated NxK list (default: the full sweep)")
@@ -144,24 +144,33 @@ def build_workload(args, tmp: Path, device: str):
         kw, n_img, n_txt = dict(n_double=3, n_single=6, hidden=1024, heads=8), 1024, 128
     else:
         kw, n_img, n_txt = dict(n_double=19, n_single=38, hidden=3072, heads=24), 4096, 512
+    with_encoder = args.workload == "flux_mistral"
     with torch.device("meta"):
         model = FluxShapedDiT(dtype=torch.bfloat16, **kw)
+        if with_encoder:        # the sharded multi-GPU configuration: a Mistral-24B-shaped text encoder in front
+            from stagehand_b200.workloads import EncoderPlusDiT, MistralShapedEncoder
+
+            model = EncoderPlusDiT(MistralShapedEncoder(dtype=torch.bfloat16), model)
     materialize_small_params(model)
     for p in model.parameters():
         p.requires_grad_(False)
+    pattern = BLOCK_PATTERNS["encoder_dit" if with_encoder else "flux"]
     fpk = tmp / "flux_shaped.fpk"
-    info = write_squareq_fpk(model, BLOCK_PATTERNS["flux"], fpk, seed=0, share_storage=not args.unique_weights)
+    info = write_squareq_fpk(model, pattern, fpk, seed=0, share_storage=not args.unique_weights)
     g = torch.Generator().manual_seed(0)
     hidden = kw["hidden"]
+    text_width = 5120 if with_encoder else hidden
     host_inputs = [
         torch.randn(1, n_img, hidden, generator=g).to(torch.bfloat16).pin_memory(),
-        torch.randn(1, n_txt, hidden, generator=g).to(torch.bfloat16).pin_memory(),
+        torch.randn(1, n_txt, text_width, generator=g).to(torch.bfloat16).pin_memory(),
         torch.randn(1, hidden, generator=g).to(torch.bfloat16).pin_memory(),
     ]
-    desc = {"workload": f"flux1-dev-shaped DiT {kw['n_double']} double + {kw['n_single']} single blocks, hidden {hidden}, "
-                        f"{n_img}+{n_txt} tokens, SquareQ INT8 per-channel",
+    name = f"flux1-dev-shaped DiT {kw['n_double']} double + {kw['n_single']} single blocks, hidden {hidden}"
+    if with_encoder:
+        name = "Mistral-24B-shaped encoder (40 layers, hidden 5120, 32 q / 8 kv heads, FFN 32768) + " + name
+    desc = {"workload": f"{name}, {n_img}+{n_txt} tokens, SquareQ INT8 per-channel",
             "int8_elements": info["elements"], "layers": info["layers"]}
-    return model, fpk, host_inputs, desc, BLOCK_PATTERNS["flux"]
+    return model, fpk, host_inputs, desc, pattern
 
 
 def make_runtime(args, model, fpk: Path, pattern: str):

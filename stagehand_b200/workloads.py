@@ -33,6 +33,7 @@ __all__ = [
     "TinyBlockModel",
     "FluxShapedDiT",
     "MistralShapedEncoder",
+    "EncoderPlusDiT",
     "LoraLinear",
     "VideoShapedDiT",
     "write_sharded_safetensors",
@@ -417,7 +418,26 @@ def write_sharded_safetensors(model: nn.Module, out_dir: str | Path, blocks_per_
     return {"tensors": tensors, "bytes": total, "shards": n_shards}
 
 
+class EncoderPlusDiT(nn.Module):
+    """A text encoder feeding a DiT: the multi-GPU sharded-streaming configuration.
+
+    ``encoder`` is a :class:`MistralShapedEncoder`, ``dit`` a :class:`FluxShapedDiT`.  The
+    encoder's output is cut to the DiT's width and used as its text stream (the real pipelines
+    put a small projection there; it is not a streamed block and is left out).
+    """
+
+    def __init__(self, encoder: nn.Module, dit: nn.Module) -> None:
+        super().__init__()
+        self.encoder = encoder
+        self.dit = dit
+
+    def forward(self, img: torch.Tensor, text: torch.Tensor, vec: torch.Tensor) -> torch.Tensor:
+        encoded = self.encoder(text)
+        return self.dit(img, encoded[..., : self.dit.hidden].contiguous(), vec)
+
+
 BLOCK_PATTERNS = {
+    "encoder_dit": r"^(encoder\.layers|dit\.double_blocks|dit\.single_blocks)\.\d+$",
     "tiny": r"^blocks\.\d+$",
     "flux": r"^(double_blocks|single_blocks)\.\d+$",
     "mistral": r"^layers\.\d+$",

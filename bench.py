@@ -66,6 +66,7 @@ def parse_args() -> argparse.Namespace:
                     help="stop the prefetch window at the last block, as the reference does (each step then starts cold)")
     ap.add_argument("--no-backward-prefetch", action="store_true",
                     help="video_train: load backward-pass blocks on demand, as the reference does")
+    ap.add_argument("--dequant-priority", type=int, default=-1, help="CUDA priority of the block kernel's stream")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--skip-delivery-only", action="store_true")
     ap.add_argument("--unique-weights", action="store_true", help="write every layer's own tensors into the slab file")
@@ -184,7 +185,8 @@ def make_runtime(args, model, fpk: Path, pattern: str):
         vram_high_watermark_mb=int(budget_mb * 0.8), vram_low_watermark_mb=int(budget_mb * 0.6),
         prefetch_window_blocks=args.prefetch_k, eviction_cooldown_steps=0,
         nan_inf_check=False, strict_bf16=False, telemetry_enabled=True, telemetry_interval_steps=0,
-        telemetry_file=os.devnull, packed_image_cache_mb=-1, prefetch_wraparound=not args.no_wraparound)
+        telemetry_file=os.devnull, packed_image_cache_mb=-1, prefetch_wraparound=not args.no_wraparound,
+        dequant_stream_priority=args.dequant_priority)
     rt = sh.StagehandRuntime(model, cfg, block_pattern=pattern, group="dit", dtype=torch.bfloat16,
                              inference_mode=True)
     converted = rt.convert_registry_to_file_backed(str(fpk))

@@ -58,6 +58,8 @@ class StagehandConfig:
     # Inference only: let the prefetch window run past the last block into the first blocks of the next
     # pass (the reference's window stops at the last block, so every pass starts with an exposed load).
     prefetch_wraparound: bool = False
+    # CUDA priority of the stream the block kernel runs on (-1 = ahead of the model's kernels, 0 = equal).
+    dequant_stream_priority: int = -1
     # Training: during the backward pass prefetch the blocks *below* the one being differentiated (the
     # reference's window only looks forward, so its backward pass loads every block on demand).
     backward_prefetch: bool = False

@@ -521,7 +521,8 @@ class StagehandScheduler:
 
         device = torch.device("cuda", torch.cuda.current_device())
         n_staging = self._config.device_staging_slabs or (self._policy.prefetch_window + 1)
-        self._streamer = Int8BlockStreamer(device, self._engine.copy_stream, n_staging)
+        self._streamer = Int8BlockStreamer(device, self._engine.copy_stream, n_staging,
+                                           dequant_priority=self._config.dequant_stream_priority)
         pool_kw = dict(on_allocation=getattr(self._budget, "invalidate", None), on_trim=self._view_cache.clear)
         if getattr(self._config, "device_pool_backend", "torch") == "vmm":
             from stagehand_b200.device_pool import VmmDeviceSlabPool

@@ -142,12 +142,13 @@ class StreamTicket:
 class Int8BlockStreamer:
     """Owns the copy stream, the dequant stream, the staging ring and the device status word."""
 
-    def __init__(self, device: torch.device, copy_stream: torch.cuda.Stream | None, n_staging: int) -> None:
+    def __init__(self, device: torch.device, copy_stream: torch.cuda.Stream | None, n_staging: int,
+                 dequant_priority: int = -1) -> None:
         self.device = device
         lib = _native.lib()
         _native.check(lib.sh_init(device.index if device.index is not None else torch.cuda.current_device()), "sh_init")
         self.copy_stream = copy_stream if copy_stream is not None else torch.cuda.Stream(device=device, priority=-1)
-        self.dequant_stream = torch.cuda.Stream(device=device, priority=-1)
+        self.dequant_stream = torch.cuda.Stream(device=device, priority=dequant_priority)
         self._n_staging = max(1, n_staging)
         self._ring: StagingRing | None = None
         self._dyn_ring: StagingRing | None = None

@@ -53,7 +53,7 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="flux", choices=["flux", "flux_small", "flux_mistral", "kernel_sweep", "video_train"])
+    ap.add_argument("--workload", default="flux", choices=["flux", "flux_small", "flux_mistral", "kernel_sweep", "video_train", "rotation", "vmm"])
     ap.add_argument("--blocks", type=int, default=0, help="video_train: number of blocks (default 48)")
     ap.add_argument("--tokens", type=int, default=6144, help="video_train: video tokens per step")
     ap.add_argument("--shapes", default="", help="kernel_sweep: comma-separated NxK list (default: the full sweep)")
@@ -563,6 +563,90 @@ def run_video_training(args) -> None:
     print(json.dumps(line), flush=True)
 
 
+def run_rotation(args) -> None:
+    """Slot-rotation engine: forward then backward sweeps over 24 blocks of 256 MiB through a 3-slot window.
+
+    Every step brings the next block in over the host link and writes the previous one back, as the
+    reference's engine does; the figure is the bytes moved per direction per second.
+    """
+    import torch
+
+    from stagehand_b200.turbo import TransferEngine
+
+    torch.cuda.set_device(0)
+    n_blocks, block_bytes, window = 24, 256 << 20, 3
+    K, W = args.steps, max(args.warmup, 0)
+    link_peak = probe_host_link()
+    engine = TransferEngine()
+    for _ in range(n_blocks):
+        engine.register_block([block_bytes])
+    engine.initialize(torch.cuda.current_device(), window)
+    source = torch.arange(block_bytes // 8, dtype=torch.int64).view(torch.uint8)
+    for i in range(n_blocks):
+        engine.stage_block(i, [source.data_ptr()])
+    slots = [torch.empty(block_bytes, dtype=torch.uint8, device="cuda") for _ in range(engine.num_gpu_slots())]
+    for i, t in enumerate(slots):
+        engine.set_slot_gpu_ptrs(i, [t.data_ptr()])
+
+    def sweeps(n: int) -> None:
+        for _ in range(n):
+            for i in range(n_blocks):
+                engine.step(i, "forward")
+            for i in reversed(range(n_blocks)):
+                engine.step(i, "backward")
+
+    sweeps(W)
+    sampler = ClockSampler(0)
+    ms, clocks = timed_region(sweeps, K, {"world": 1, "rank": 0}, sampler)
+    engine.drain()
+    check = torch.empty(block_bytes, dtype=torch.uint8)
+    import ctypes
+
+    ctypes.memmove(check.data_ptr(), engine.cpu_ptr(n_blocks - 1, 0), block_bytes)
+    intact = bool(torch.equal(check, source))
+    engine.close()
+    per_sweep_pair = 2 * n_blocks * block_bytes          # bytes brought in (and, minus the window, written back)
+    gbs = per_sweep_pair * K / (ms / 1e3) / 1e9
+    print(json.dumps({"metric": "rotation_h2d_GBps", "value": gbs, "unit": UNIT, "n_gpus": 1, "steps": K, "warmup": W,
+                      "ms_per_step": ms / K, "higher_is_better": True, "dtype": "u8", "data": "synthetic",
+                      "config": {"workload": f"slot rotation, {n_blocks} blocks x {block_bytes >> 20} MiB, window {window}, "
+                                             "one forward and one backward sweep per step"},
+                      "host_link": {"peak_gbs": link_peak, "frac": gbs / link_peak}, "clocks": clocks,
+                      "data_intact_after_round_trips": intact}), flush=True)
+
+
+def run_vmm(args) -> None:
+    """Virtual-memory slab allocator: cost of making a region resident (map) and of evicting under a ceiling."""
+    import torch
+
+    from stagehand_b200.vmm import SlabAllocator
+
+    torch.cuda.set_device(0)
+    region, n_regions = 256 << 20, 32
+    alloc = SlabAllocator(device=torch.cuda.current_device(), ceiling_mb=(region >> 20) * 8)     # room for 8 of 32
+    slab = alloc.create_slab(region * n_regions)
+    regions = [alloc.define_region(slab, i * region, region) for i in range(n_regions)]
+    stream = torch.cuda.current_stream().cuda_stream
+    out = {}
+    for label, order in (("first_touch_map", range(8)), ("map_with_eviction", range(8, 32)), ("resident_hit", [31] * 200)):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        n = 0
+        for i in order:
+            h = alloc.ensure_resident(slab, regions[i], stream)
+            h.release()
+            n += 1
+        torch.cuda.synchronize()
+        out[label + "_us"] = (time.perf_counter() - t0) / n * 1e6
+    stats = alloc.stats()
+    alloc.destroy_slab(slab)
+    alloc.close()
+    print(json.dumps({"metric": "vmm_ensure_resident_us", "value": out["map_with_eviction_us"], "unit": "us",
+                      "n_gpus": 1, "higher_is_better": False, "data": "synthetic",
+                      "config": {"workload": f"{n_regions} regions x {region >> 20} MiB in one slab, ceiling 8 regions"},
+                      "detail": out, "stats": stats}), flush=True)
+
+
 def kernel_profile(native, timeout_ms: int = 120_000) -> dict:
     import ctypes
 
@@ -590,6 +674,10 @@ def main() -> None:
     if args.workload == "kernel_sweep":
         if int(os.environ.get("RANK", "0")) == 0:
             run_kernel_sweep(args)
+        return
+    if args.workload in ("rotation", "vmm"):      # the engines beside the path: single-GPU measurements
+        if int(os.environ.get("RANK", "0")) == 0:
+            (run_rotation if args.workload == "rotation" else run_vmm)(args)
         return
     if args.workload == "video_train":      # single-GPU configuration; other ranks have nothing to do
         if int(os.environ.get("RANK", "0")) == 0:
@@ -647,7 +735,9 @@ def main() -> None:
             out = {"ms_total": ms, "clocks": clocks, "profile": prof, "stats": stats, "desc": desc,
                    "converted": converted, "delivered_bytes": last.h2d_bytes, "link_bytes": last.link_bytes,
                    "peer_bytes": last.peer_bytes, "hits": last.prefetch_hits, "misses": last.prefetch_misses,
-                   "evictions": last.evictions, "input_bytes": sum(t.numel() * t.element_size() for t in host_inputs)}
+                   "evictions": last.evictions, "soft_hits": last.soft_hits,
+                   "host_stall_ms": float(getattr(last, "stall_time_ms", 0.0)),
+                   "input_bytes": sum(t.numel() * t.element_size() for t in host_inputs)}
             if not args.skip_delivery_only:
                 go(1, compute=False, io=False)
                 kernel_profile(native)
@@ -732,8 +822,14 @@ def compose_line(args, world: int, results: dict, peaks: dict, link_peak: float,
         "gpu_launches": v["stats"]["kernel_launches"],
         "roofline": roof(v["profile"]),
         "cpu_baseline": cpu,
-        "telemetry": {"value": {k: v[k] for k in ("hits", "misses", "evictions", "kernel_status", "vram_pool")},
-                      "e2e": {k: e[k] for k in ("hits", "misses", "evictions", "kernel_status", "vram_pool")}},
+        # hits = resident at use; soft_hits = in flight and already complete at use (no wait anywhere); the rest of the
+        # misses were in flight or loaded on demand and the compute stream waited for them on the device.
+        # exposed_delivery_ms = what streaming from the source adds to a forward whose weights are already in HBM.
+        "telemetry": {"value": {k: v[k] for k in ("hits", "soft_hits", "misses", "evictions", "host_stall_ms",
+                                                  "kernel_status", "vram_pool")},
+                      "e2e": {k: e[k] for k in ("hits", "soft_hits", "misses", "evictions", "host_stall_ms",
+                                                "kernel_status", "vram_pool")},
+                      "exposed_delivery_ms": max(0.0, (e["ms_total"] - v["ms_total"]) / K)},
         "setup_s": setup_s,
     }
     if world > 1:

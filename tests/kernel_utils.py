@@ -1,8 +1,6 @@
 """Helpers shared by the GPU tests: build a packed image by hand and run the block kernel through the C ABI."""
 from __future__ import annotations
 
-import ctypes
-
 import numpy as np
 import torch
 

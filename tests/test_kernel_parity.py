@@ -7,7 +7,7 @@ import pytest
 import torch
 
 from conftest import GOLDEN
-from kernel_utils import DT_SIZE, HandImage, run_block
+from kernel_utils import HandImage, run_block
 from oracle import squareq_oracle as oracle
 from stagehand_b200 import _native
 

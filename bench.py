@@ -64,6 +64,8 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--no-fused", action="store_true", help="multi-GPU: copy-engine pull + kernel instead of the fused kernel")
     ap.add_argument("--no-wraparound", action="store_true",
                     help="stop the prefetch window at the last block, as the reference does (each step then starts cold)")
+    ap.add_argument("--training-lookahead", action="store_true",
+                    help="video_train: plan prefetch and eviction against the up-then-down order of a training step")
     ap.add_argument("--no-backward-prefetch", action="store_true",
                     help="video_train: load backward-pass blocks on demand, as the reference does")
     ap.add_argument("--dequant-priority", type=int, default=-1, help="CUDA priority of the block kernel's stream")
@@ -481,7 +483,7 @@ def run_video_training(args) -> None:
             vram_high_watermark_mb=int(budget_mb * 0.8), vram_low_watermark_mb=int(budget_mb * 0.6),
             prefetch_window_blocks=args.prefetch_k, eviction_cooldown_steps=0, nan_inf_check=False, strict_bf16=False,
             telemetry_enabled=True, telemetry_interval_steps=0, telemetry_file=os.devnull, packed_image_cache_mb=-1,
-            backward_prefetch=not args.no_backward_prefetch)
+            backward_prefetch=not args.no_backward_prefetch, training_lookahead=args.training_lookahead)
         rt = sh.StagehandRuntime(model, cfg, block_pattern=BLOCK_PATTERNS["video"], group="dit", dtype=torch.bfloat16,
                                  inference_mode=False)
         converted = rt.convert_registry_to_file_backed_sharded(str(tmp / "ckpt"))
@@ -551,6 +553,7 @@ def run_video_training(args) -> None:
                        "frozen_weights": info["bytes"] // 2, "converted_params": converted,
                        "vram_budget_gb": budget_gb, "prefetch_k": args.prefetch_k,
                        "backward_prefetch": not args.no_backward_prefetch,
+                       "training_lookahead": args.training_lookahead,
                        "l2": "weights larger than L2; no flush",
                        "value_source": "same timed region as e2e (weights in page-locked host images; the budget is below the model size)"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": stats["kernel_launches"], "roofline": roofline,

@@ -63,6 +63,10 @@ class StagehandConfig:
     # Training: during the backward pass prefetch the blocks *below* the one being differentiated (the
     # reference's window only looks forward, so its backward pass loads every block on demand).
     backward_prefetch: bool = False
+    # Training: plan prefetch and eviction against the order a training step really uses the blocks in
+    # (up, then down again): prefetch the next blocks that are not resident however far ahead they are,
+    # evict the block whose next use is farthest away.  Includes backward_prefetch.
+    training_lookahead: bool = False
     # Where the block slabs in VRAM come from: "torch" (caching allocator) or "vmm" (the C++ virtual-memory
     # slab allocator: parked slabs can be unmapped under `vmm_ceiling_mb` without fragmenting anything).
     device_pool_backend: str = "torch"

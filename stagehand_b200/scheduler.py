@@ -453,10 +453,42 @@ class StagehandScheduler:
         cur = self._current_index
         return [i for i in range(cur - 1, cur - 1 - self._policy.prefetch_window, -1) if i >= 0]
 
+    def _planned_accesses(self) -> list[int] | None:
+        """Upcoming block indices of a training step in the order they will be used, or None.
+
+        A training step walks the blocks up and then down again.  With ``training_lookahead`` the
+        scheduler plans against that order: from block *c* of the forward pass the sequence is
+        ``c+1 .. T-1, T-1 .. 0``; from block *c* of the backward pass it is ``c-1 .. 0``.
+        """
+        if self._inference_mode or not self._config.training_lookahead or self._current_index < 0:
+            return None
+        cur, total = self._current_index, self._total_blocks
+        if self._backward_phase:
+            return list(range(cur - 1, -1, -1))
+        return list(range(cur + 1, total)) + list(range(total - 1, -1, -1))
+
+    def _lookahead_window(self, accesses: list[int]) -> list[int]:
+        """The first ``prefetch_window`` blocks of *accesses* that are neither resident nor in flight."""
+        wanted: list[int] = []
+        seen: set[int] = set()
+        for idx in accesses:
+            if idx in seen:
+                continue
+            seen.add(idx)
+            if self._residency.get_state(self._block_ids[idx]) in (BlockState.GPU_READY, BlockState.PREFETCHING):
+                continue
+            wanted.append(idx)
+            if len(wanted) >= self._policy.prefetch_window:
+                break
+        return wanted
+
     def _prefetch_ahead(self) -> None:
         states = _ResidencyStates(self._residency, self._block_ids)
         backward = self._backward_window()
-        if backward is not None:
+        planned = self._planned_accesses()
+        if planned is not None:
+            wanted = self._lookahead_window(planned)
+        elif backward is not None:
             wanted = backward
         else:
             wanted = list(self._policy.blocks_to_prefetch(self._cursor - 1, self._total_blocks, states))
@@ -820,7 +852,15 @@ class StagehandScheduler:
         window_start = max(self._cursor - 1, 0)
         wrap = self._wraparound_active()
         backward = self._backward_window()
-        if backward is not None:
+        planned = self._planned_accesses()
+        position: dict[int, int] = {}
+        if planned is not None:
+            for at, idx in enumerate(planned):
+                position.setdefault(idx, at)
+            protected = {self._block_ids[i] for i in planned[: self._policy.prefetch_window]}
+            protected |= {self._block_ids[i] for i in self._lookahead_window(planned)}
+            backward = None
+        elif backward is not None:
             protected = {self._block_ids[i] for i in backward}
         else:
             protected = {
@@ -833,6 +873,13 @@ class StagehandScheduler:
             if block_id in protected:
                 continue
             entry = self._registry.get(block_id)
+            if planned is not None:
+                # time until the block is used again; one the rest of this step does not touch waits for
+                # the next step's forward pass
+                order = self._index_of[block_id]
+                distance = position.get(order, len(planned) + order) + 1
+                ranked.append((float(distance * entry.size_bytes), block_id))
+                continue
             if backward is not None:
                 # Going down: blocks below the current one are needed soon; those at or above it are done
                 # until the next forward pass reaches them again.

@@ -258,21 +258,22 @@ def test_gpu_backward_pass_prefetches_downwards(tmp_path: Path) -> None:
 
     from stagehand_b200.workloads import VideoShapedDiT, write_sharded_safetensors
 
-    demand: dict[bool, int] = {}
-    grads: dict[bool, list[torch.Tensor]] = {}
-    for enabled in (False, True):
+    demand: dict[object, int] = {}
+    grads: dict[object, list[torch.Tensor]] = {}
+    for enabled in (False, True, "lookahead"):
         torch.manual_seed(0)
         model = VideoShapedDiT(n_blocks=6, hidden=512, heads=8, ffn=2048, rank=4, dtype=torch.float32)
         model.init_adapters(seed=5, std=0.05)
         for name, p in model.named_parameters():
             p.requires_grad_("lora" in name)
-        ckpt = tmp_path / f"ckpt{int(enabled)}"
+        ckpt = tmp_path / f"ckpt_{enabled}"
         write_sharded_safetensors(model, ckpt, blocks_per_shard=4, seed=1, std=0.05, dtype=torch.float32)
         gc.collect()
         base_mb = int(torch.cuda.memory_allocated() >> 20)
         # a block is 16.8 MB: room for about three of the six
         cfg = sh.StagehandConfig(pinned_pool_mb=64, pinned_slab_mb=32, telemetry_enabled=False, nan_inf_check=False,
-                                 prefetch_window_blocks=1, eviction_cooldown_steps=0, backward_prefetch=enabled,
+                                 prefetch_window_blocks=1, eviction_cooldown_steps=0, backward_prefetch=enabled is True,
+                                 training_lookahead=enabled == "lookahead",
                                  vram_high_watermark_mb=base_mb + 75, vram_low_watermark_mb=base_mb + 40)
         rt = sh.StagehandRuntime(model, cfg, block_pattern=r"^blocks\.\d+$", dtype=torch.float32, inference_mode=False)
         rt.convert_registry_to_file_backed_sharded(str(ckpt))
@@ -299,5 +300,7 @@ def test_gpu_backward_pass_prefetches_downwards(tmp_path: Path) -> None:
         del model, rt
     assert demand[False] >= 4                 # the reference's window never looks down: loads on demand
     assert demand[True] <= demand[False] // 2
-    for a, b in zip(grads[False], grads[True]):
-        assert torch.equal(a, b)              # the same arithmetic either way
+    assert demand["lookahead"] <= demand[False] // 2
+    for mode in (True, "lookahead"):
+        for a, b in zip(grads[False], grads[mode]):
+            assert torch.equal(a, b)          # the same arithmetic whatever the schedule

@@ -202,6 +202,10 @@ class StagehandScheduler:
         self._empties: dict[torch.dtype, torch.Tensor] = {}
         self._packed_files: dict[str, Any] = {}
         self._evicted_copies: dict[str, dict[str, torch.Tensor]] = {}   # block -> name -> CPU copy in the runtime dtype
+        # Training: trainable parameters (and their gradients) leave an evicted block through page-locked
+        # buffers by an asynchronous copy; the event says when the host may read them.
+        self._save_buffers: dict[tuple[str, str, str], torch.Tensor] = {}
+        self._pending_saves: dict[str, torch.cuda.Event] = {}
 
     # ── step lifecycle ───────────────────────────────────────────────
 
@@ -227,6 +231,7 @@ class StagehandScheduler:
         self._engine.reap()
         self._reap_deferred_slabs()
         self._reconcile_file_backed_grads()
+        self._await_saves()              # the caller's optimiser reads parameters and gradients next
         self._telemetry.end_step()
 
     def enter_backward_phase(self) -> None:
@@ -503,6 +508,14 @@ class StagehandScheduler:
             block_id = self._ordered_blocks[idx].block_id
             if self._residency.get_state(block_id) in (BlockState.GPU_READY, BlockState.PREFETCHING):
                 continue
+            if planned is not None:
+                # look-ahead schedule: the block must fit under the high watermark; room is made only by
+                # giving up blocks whose next use is farther away than this one's
+                need = self._ordered_blocks[idx].size_bytes
+                if self._budget.headroom_mb() * 1024 * 1024 <= need:
+                    self._run_eviction(ignore_cooldown=True, needed_before=planned.index(idx), room_bytes=need)
+                if self._budget.headroom_mb() * 1024 * 1024 <= need:
+                    break
             if not self._budget.can_prefetch():
                 break
             self._load_block_to_gpu(block_id, speculative=True)
@@ -514,6 +527,7 @@ class StagehandScheduler:
             return
         entry = self._registry.get(block_id)
         res = self._residency.get_entry(block_id)
+        self._await_saves(block_id)      # its trainable parameters are about to be read on the host
 
         if entry.eriquant_backed:
             raise TransferError(f"block {block_id!r} is eriquant-backed; that adapter path is not part of this runtime")
@@ -845,8 +859,15 @@ class StagehandScheduler:
 
     # ── eviction ─────────────────────────────────────────────────────
 
-    def _run_eviction(self, ignore_cooldown: bool = False) -> None:
-        """Evict unreferenced blocks outside the prefetch window, best score first, until below the low watermark."""
+    def _run_eviction(self, ignore_cooldown: bool = False, needed_before: int | None = None,
+                      room_bytes: int = 0) -> None:
+        """Evict unreferenced blocks outside the prefetch window, best score first, until below the low watermark.
+
+        Under the training look-ahead schedule eviction is one for one instead: it stops as soon as usage is
+        *room_bytes* below the high watermark, and with *needed_before* (a position in the planned access
+        order) it only takes blocks whose next use lies after that position -- making room for a block never
+        costs one that is needed sooner.
+        """
         cooldown = 0 if ignore_cooldown else self._policy.eviction_cooldown_steps
         candidates = self._residency.eviction_candidates(self._current_step, cooldown)
         window_start = max(self._cursor - 1, 0)
@@ -878,7 +899,9 @@ class StagehandScheduler:
                 # the next step's forward pass
                 order = self._index_of[block_id]
                 distance = position.get(order, len(planned) + order) + 1
-                ranked.append((float(distance * entry.size_bytes), block_id))
+                if needed_before is not None and distance <= needed_before + 1:
+                    continue
+                ranked.append((float(distance), block_id))
                 continue
             if backward is not None:
                 # Going down: blocks below the current one are needed soon; those at or above it are done
@@ -893,6 +916,8 @@ class StagehandScheduler:
         for _score, block_id in ranked:
             if self._budget.below_low_watermark():
                 break
+            if planned is not None and self._budget.headroom_mb() * 1024 * 1024 > room_bytes:
+                break
             self._evict_block(block_id, save_back=not self._inference_mode)
             self._telemetry.record_eviction()
 
@@ -905,6 +930,33 @@ class StagehandScheduler:
             self._engine._pool.release(res.host_slab)
         res.host_slab = None
         res.param_layout = None
+
+    def _save_async(self, block_id: str, name: str, kind: str, live: torch.Tensor) -> torch.Tensor:
+        """Copy *live* (on the GPU) into this parameter's page-locked buffer without waiting for it.
+
+        The copy is queued on the current stream behind the kernels that produced the value; the
+        caller records the block's save event afterwards.  The buffer is this parameter's own and is
+        only rewritten at its next eviction, when the parameter points into a VRAM slab again.
+        """
+        key = (block_id, name, kind)
+        buf = self._save_buffers.get(key)
+        with torch.inference_mode(False):
+            if buf is None or buf.shape != live.shape or buf.dtype != live.dtype:
+                buf = torch.empty(live.shape, dtype=live.dtype, pin_memory=True)
+                self._save_buffers[key] = buf
+            buf.copy_(live.detach(), non_blocking=True)
+        return buf
+
+    def _await_saves(self, block_id: str | None = None) -> None:
+        """Block the host until the asynchronous save of *block_id* (or of every block) has landed."""
+        if block_id is not None:
+            event = self._pending_saves.pop(block_id, None)
+            if event is not None:
+                event.synchronize()
+            return
+        for event in self._pending_saves.values():
+            event.synchronize()
+        self._pending_saves.clear()
 
     def _evict_block(self, block_id: str, save_back: bool = False) -> None:
         """Drop *block_id* from VRAM.
@@ -923,6 +975,7 @@ class StagehandScheduler:
         if module is not None and res.param_layout is not None:
             if source_backed:
                 mutable = set(entry.module_param_names)
+                saved_async = False
                 keep_on_gpu = self._defer_backward_eviction and not self._backward_phase
                 # Inference: a module-owned parameter's value does not change while it sits in VRAM, so the
                 # host copy made at its first eviction stands in for every later device-to-host read
@@ -938,6 +991,10 @@ class StagehandScheduler:
                                 and kept.shape == live.shape and staged_ptrs.get(name) == kept.data_ptr()):
                             _set_param_data(module, name, kept)
                             continue
+                        if host_copies is None and not keep_on_gpu and live.device.type == "cuda":
+                            saved_async = True          # training: no host wait at eviction
+                            _set_param_data(module, name, self._save_async(block_id, name, "data", live))
+                            continue
                         target = live.device if keep_on_gpu else torch.device("cpu")
                         with torch.inference_mode(False):
                             moved = live.to(target).clone()
@@ -952,7 +1009,11 @@ class StagehandScheduler:
                 if save_back:
                     for name, param in module.named_parameters():
                         if name in mutable and param.grad is not None and param.grad.device.type != "cpu":
-                            param.grad = param.grad.to("cpu", non_blocking=True)
+                            saved_async = True
+                            param.grad = self._save_async(block_id, name, "grad", param.grad)
+                if saved_async:
+                    self._pending_saves[block_id] = torch.cuda.Event()
+                    self._pending_saves[block_id].record()
             else:
                 for name, _shape, _dtype, _off, _numel in res.param_layout:
                     _set_param_data(module, name, _get_param_data(module, name).to("cpu").clone())

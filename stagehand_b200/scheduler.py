@@ -511,7 +511,8 @@ class StagehandScheduler:
             if planned is not None:
                 # look-ahead schedule: the block must fit under the high watermark; room is made only by
                 # giving up blocks whose next use is farther away than this one's
-                need = self._ordered_blocks[idx].size_bytes
+                slack = (self._budget.high_watermark_mb - self._budget.low_watermark_mb) * 1024 * 1024 // 2
+                need = self._ordered_blocks[idx].size_bytes + slack      # headroom left for activations
                 if self._budget.headroom_mb() * 1024 * 1024 <= need:
                     self._run_eviction(ignore_cooldown=True, needed_before=planned.index(idx), room_bytes=need)
                 if self._budget.headroom_mb() * 1024 * 1024 <= need:

@@ -371,6 +371,9 @@ class StagehandScheduler:
         self._squareq_layers.clear()
         self._module_param_caches.clear()
         self._evicted_copies.clear()
+        if self._pending_saves:
+            self._await_saves()
+        self._save_buffers.clear()       # parameters that still point at a buffer keep it alive themselves
 
     # ── per-block hooks ──────────────────────────────────────────────
 

@@ -68,6 +68,8 @@ def parse_args() -> argparse.Namespace:
                     help="video_train: plan prefetch and eviction against the up-then-down order of a training step")
     ap.add_argument("--no-backward-prefetch", action="store_true",
                     help="video_train: load backward-pass blocks on demand, as the reference does")
+    ap.add_argument("--peer-ctas-per-sm", type=int, default=0,
+                    help="multi-GPU: CTAs per SM a block-kernel launch that reads peer memory may occupy (0 = no cap)")
     ap.add_argument("--dequant-priority", type=int, default=-1, help="CUDA priority of the block kernel's stream")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--skip-delivery-only", action="store_true")
@@ -717,7 +719,8 @@ def main() -> None:
                 from stagehand_b200.sharded import DeviceImageStore
 
                 store = DeviceImageStore(rt, rank=rank, world=world, fused=not args.no_fused,
-                                         layout=args.layout if world > 1 else "owner")
+                                         layout=args.layout if world > 1 else "owner",
+                                         peer_ctas_per_sm=args.peer_ctas_per_sm)
             device_inputs = [t.cuda() for t in host_inputs]
             host_io = name == "e2e"
             step = [0]

@@ -236,6 +236,16 @@ int32_t sh_stream_block_async(const ShParamDesc* descs, int32_t n_descs,
                               uint64_t ev_copied, uint64_t ev_ready, int32_t* status_dev);
 
 /*
+ * Cap, in CTAs per SM, on block-kernel launches that read another GPU's memory
+ * (descriptors flagged SH_DESC_PEER_SOURCE); 0 lifts it (the default).  Such a
+ * launch runs at the pace of its NVLink reads; capped, it leaves most of every
+ * SM to the kernels of the model running beside it and walks its tiles
+ * grid-stride.  Results are identical either way.  No counterpart in the
+ * reference, which has no multi-GPU path.  Negative values are treated as 0.
+ */
+int32_t sh_set_peer_ctas_per_sm(int32_t ctas_per_sm);
+
+/*
  * Per-launch device timing of the block kernel (CUDA events on the launching
  * stream).  While enabled every launch is bracketed by a pair of timing events;
  * sh_profile_collect waits for them (bounded) and returns the sums since the

@@ -124,6 +124,7 @@ _SIGNATURES: dict[str, list] = {
     "sh_vmm_destroy_slab": [c_uint64, c_int32],
     "sh_vmm_stats": [c_uint64, POINTER(ShVmmStats)],
     "sh_vmm_last_error": [c_char_p, c_int32],
+    "sh_set_peer_ctas_per_sm": [c_int32],
     "sh_profile_enable": [c_int32],
     "sh_profile_collect": [POINTER(c_double), POINTER(c_int64), POINTER(c_int64), POINTER(c_int64), c_int32],
 }

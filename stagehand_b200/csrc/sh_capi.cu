@@ -428,6 +428,11 @@ int32_t sh_stream_block_async(const ShParamDesc* descs, int32_t n_descs, const v
     return SH_OK;
 }
 
+int32_t sh_set_peer_ctas_per_sm(int32_t ctas_per_sm) {
+    sq::set_peer_ctas_per_sm(ctas_per_sm);
+    return SH_OK;
+}
+
 int32_t sh_profile_enable(int32_t on) {
     g_prof_on.store(on ? 1 : 0);
     return SH_OK;

@@ -17,6 +17,8 @@
 // and writes one 32-byte store per load (two 16-byte stores when the destination is not 32-byte aligned).
 #include "sq_block_kernel.cuh"
 
+#include <atomic>
+
 #include <cstdio>
 #include <cstring>
 #include <cuda_bf16.h>
@@ -201,7 +203,7 @@ __device__ __forceinline__ uint32_t tile_row_of(uint32_t t, uint32_t spr, uint64
 
 template <typename OutT, bool HasZp, bool Dense>
 __device__ __forceinline__ void dequant_vec_tile(const DescDev& D, int64_t local_tile, float* s_scale, float* s_zp,
-                                                 uint64_t* s_bar, int32_t* status) {
+                                                 uint64_t* s_bar, int32_t* status, bool may_stage) {
     const uint32_t spr = static_cast<uint32_t>(D.segs_per_row);
     const uint64_t magic = D.row_magic;
     const int64_t total_segs = D.rows * static_cast<int64_t>(spr);
@@ -260,7 +262,7 @@ __device__ __forceinline__ void dequant_vec_tile(const DescDev& D, int64_t local
     const uint32_t n_stage = (lead + rows_in_tile + 3u) & ~3u;
     // Staging pays when a tile spans many scale rows (short rows); with long rows a tile needs a
     // handful of scales and plain cached loads are cheaper than a barrier round trip.
-    bool staged = (D.flags & kFlagBulkScales) != 0 && rows_in_tile >= kStageMinRows && n_stage <= kSmemRows;
+    bool staged = may_stage && (D.flags & kFlagBulkScales) != 0 && rows_in_tile >= kStageMinRows && n_stage <= kSmemRows;
     if (staged) {
         if (threadIdx.x == 0) {
             mbar_init(s_bar, 1);
@@ -378,10 +380,15 @@ __global__ void __launch_bounds__(kThreads, SQ_MIN_CTAS_PER_SM) sq_block_kernel(
     __shared__ alignas(16) float s_zp[kSmemRows];
     __shared__ alignas(8) uint64_t s_bar;
 
+    // One tile per CTA when the grid covers the launch; a capped grid (launches that read a peer GPU's
+    // memory, see launch_plan) walks the tiles grid-stride.  Only a CTA with a single tile stages scales
+    // through shared memory: the barrier is initialised once per CTA.
+    const uint32_t total = static_cast<uint32_t>(plan.total_tiles);
+    const bool single = gridDim.x >= total;
+    for (uint32_t work = blockIdx.x; work < total; work += gridDim.x) {
     const uint32_t tile = plan.tile_stride == 1u
-                              ? blockIdx.x
-                              : static_cast<uint32_t>((static_cast<uint64_t>(blockIdx.x) * plan.tile_stride) %
-                                                      static_cast<uint32_t>(plan.total_tiles));
+                              ? work
+                              : static_cast<uint32_t>((static_cast<uint64_t>(work) * plan.tile_stride) % total);
     // descriptor of this tile: the last d with tile_begin[d] <= tile (binary search, uniform across the CTA)
     int d = 0;
     for (int hi = plan.n_desc; hi - d > 1;) {
@@ -394,11 +401,11 @@ __global__ void __launch_bounds__(kThreads, SQ_MIN_CTAS_PER_SM) sq_block_kernel(
     switch (D.path) {
         case kPathDequantVec:
             if (D.flags & kFlagDense) {
-                if (D.zp != nullptr) dequant_vec_tile<OutT, true, true>(D, local_tile, s_scale, s_zp, &s_bar, status);
-                else                 dequant_vec_tile<OutT, false, true>(D, local_tile, s_scale, s_zp, &s_bar, status);
+                if (D.zp != nullptr) dequant_vec_tile<OutT, true, true>(D, local_tile, s_scale, s_zp, &s_bar, status, single);
+                else                 dequant_vec_tile<OutT, false, true>(D, local_tile, s_scale, s_zp, &s_bar, status, single);
             } else {
-                if (D.zp != nullptr) dequant_vec_tile<OutT, true, false>(D, local_tile, s_scale, s_zp, &s_bar, status);
-                else                 dequant_vec_tile<OutT, false, false>(D, local_tile, s_scale, s_zp, &s_bar, status);
+                if (D.zp != nullptr) dequant_vec_tile<OutT, true, false>(D, local_tile, s_scale, s_zp, &s_bar, status, single);
+                else                 dequant_vec_tile<OutT, false, false>(D, local_tile, s_scale, s_zp, &s_bar, status, single);
             }
             break;
         case kPathDequantScalar: dequant_scalar_tile<OutT>(D, local_tile); break;
@@ -412,11 +419,38 @@ __global__ void __launch_bounds__(kThreads, SQ_MIN_CTAS_PER_SM) sq_block_kernel(
             if (threadIdx.x == 0 && status != nullptr) atomicOr(status, kStatusBadPath);
             break;
     }
+    }
+}
+
+// CTAs per SM a launch that reads another GPU's memory may occupy (0 = no cap).  Such a launch runs at the
+// pace of the NVLink reads, several times longer than a local one; left uncapped it holds every thread slot
+// of every SM for that time and the model's own kernels queue behind it.
+static std::atomic<int> g_peer_ctas_per_sm{0};
+static std::atomic<int> g_sm_count{0};
+
+void set_peer_ctas_per_sm(int n) { g_peer_ctas_per_sm.store(n < 0 ? 0 : n); }
+int peer_ctas_per_sm() { return g_peer_ctas_per_sm.load(); }
+
+static int sm_count() {
+    int n = g_sm_count.load();
+    if (n == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+            n = 148;
+        g_sm_count.store(n);
+    }
+    return n;
 }
 
 cudaError_t launch_plan(const BlockPlan& plan, int out_dtype, cudaStream_t stream, int32_t* status_dev) {
     if (plan.total_tiles <= 0) return cudaSuccess;
-    const dim3 grid(static_cast<unsigned>(plan.total_tiles));
+    unsigned ctas = static_cast<unsigned>(plan.total_tiles);
+    const int cap = g_peer_ctas_per_sm.load();
+    if (cap > 0 && plan.tile_stride != 1u) {     // a scattered launch is one that reads peer memory
+        const unsigned limit = static_cast<unsigned>(cap) * static_cast<unsigned>(sm_count());
+        if (ctas > limit) ctas = limit;
+    }
+    const dim3 grid(ctas);
     const dim3 block(kThreads);
     switch (out_dtype) {
         case SH_DT_BF16: sq_block_kernel<__nv_bfloat16><<<grid, block, 0, stream>>>(plan, status_dev); break;

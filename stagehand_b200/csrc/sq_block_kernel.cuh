@@ -91,4 +91,8 @@ int build_plans(const ShParamDesc* descs, int n, const void* packed, size_t pack
 // Launches one plan on `stream`.
 cudaError_t launch_plan(const BlockPlan& plan, int out_dtype, cudaStream_t stream, int32_t* status_dev);
 
+// Cap, in CTAs per SM, on launches that read another GPU's memory (0 = none).
+void set_peer_ctas_per_sm(int n);
+int peer_ctas_per_sm();
+
 }  // namespace sq

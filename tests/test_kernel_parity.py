@@ -169,6 +169,29 @@ def test_peer_flag_uses_plain_loads_and_matches() -> None:
     _assert_same(out[off : off + ref.size], ref, "bf16")
 
 
+@pytest.mark.parametrize("cap", [1, 2])
+def test_capped_peer_launch_walks_its_tiles_grid_stride(cap: int) -> None:
+    """With a CTA cap a peer-reading launch has fewer CTAs than tiles; every tile is still written, bit-exact."""
+    rng = np.random.default_rng(11)
+    lib = _native.lib()
+    img = HandImage()
+    cases = []
+    for rows, cols, with_zp in ((3000, 4096, False), (1537, 2048, True), (40000, 64, False), (9, 1000, True)):
+        q = rng.integers(-128, 128, size=(rows, cols), dtype=np.int8)
+        scale = np.exp(rng.standard_normal(rows)).astype(np.float32)
+        zp = rng.standard_normal(rows).astype(np.float32) if with_zp else None
+        cases.append((img.add_dequant(q, scale, zp, rows, cols, "bf16", peer=True), q, scale, zp, rows, cols))
+    try:
+        _native.check(lib.sh_set_peer_ctas_per_sm(cap))
+        out, status = run_block(img, "bf16")      # ~2700 tiles against at most 148 * cap CTAs
+    finally:
+        _native.check(lib.sh_set_peer_ctas_per_sm(0))
+    assert status == 0
+    for off, q, scale, zp, rows, cols in cases:
+        ref = oracle.dequant_rows(q, scale, zp, rows, cols, "bf16")
+        _assert_same(out[off : off + ref.size], ref, "bf16")
+
+
 def test_bad_descriptors_are_rejected_before_launch() -> None:
     lib = _native.lib()
     _native.check(lib.sh_init(torch.cuda.current_device()))

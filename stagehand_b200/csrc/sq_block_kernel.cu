@@ -374,8 +374,9 @@ __device__ __forceinline__ void copy_zero_tile(const DescDev& D, int64_t local_t
 
 // ── the kernel ───────────────────────────────────────────────────────────
 
-template <typename OutT>
-__global__ void __launch_bounds__(kThreads, SQ_MIN_CTAS_PER_SM) sq_block_kernel(const __grid_constant__ BlockPlan plan, int32_t* status) {
+template <typename OutT, bool GridStride>
+__global__ void __launch_bounds__(kThreads, GridStride ? 4 : SQ_MIN_CTAS_PER_SM)
+sq_block_kernel(const __grid_constant__ BlockPlan plan, int32_t* status) {
     __shared__ alignas(16) float s_scale[kSmemRows];
     __shared__ alignas(16) float s_zp[kSmemRows];
     __shared__ alignas(8) uint64_t s_bar;
@@ -384,8 +385,8 @@ __global__ void __launch_bounds__(kThreads, SQ_MIN_CTAS_PER_SM) sq_block_kernel(
     // memory, see launch_plan) walks the tiles grid-stride.  Only a CTA with a single tile stages scales
     // through shared memory: the barrier is initialised once per CTA.
     const uint32_t total = static_cast<uint32_t>(plan.total_tiles);
-    const bool single = gridDim.x >= total;
-    for (uint32_t work = blockIdx.x; work < total; work += gridDim.x) {
+    constexpr bool single = !GridStride;
+    for (uint32_t work = blockIdx.x; work < total; work += GridStride ? gridDim.x : total) {
     const uint32_t tile = plan.tile_stride == 1u
                               ? work
                               : static_cast<uint32_t>((static_cast<uint64_t>(work) * plan.tile_stride) % total);
@@ -451,11 +452,20 @@ cudaError_t launch_plan(const BlockPlan& plan, int out_dtype, cudaStream_t strea
         if (ctas > limit) ctas = limit;
     }
     const dim3 grid(ctas);
+    if (ctas < static_cast<unsigned>(plan.total_tiles)) {
+        switch (out_dtype) {
+            case SH_DT_BF16: sq_block_kernel<__nv_bfloat16, true><<<grid, dim3(kThreads), 0, stream>>>(plan, status_dev); break;
+            case SH_DT_F16:  sq_block_kernel<__half, true><<<grid, dim3(kThreads), 0, stream>>>(plan, status_dev); break;
+            case SH_DT_F32:  sq_block_kernel<float, true><<<grid, dim3(kThreads), 0, stream>>>(plan, status_dev); break;
+            default: return cudaErrorInvalidValue;
+        }
+        return cudaGetLastError();
+    }
     const dim3 block(kThreads);
     switch (out_dtype) {
-        case SH_DT_BF16: sq_block_kernel<__nv_bfloat16><<<grid, block, 0, stream>>>(plan, status_dev); break;
-        case SH_DT_F16:  sq_block_kernel<__half><<<grid, block, 0, stream>>>(plan, status_dev); break;
-        case SH_DT_F32:  sq_block_kernel<float><<<grid, block, 0, stream>>>(plan, status_dev); break;
+        case SH_DT_BF16: sq_block_kernel<__nv_bfloat16, false><<<grid, block, 0, stream>>>(plan, status_dev); break;
+        case SH_DT_F16:  sq_block_kernel<__half, false><<<grid, block, 0, stream>>>(plan, status_dev); break;
+        case SH_DT_F32:  sq_block_kernel<float, false><<<grid, block, 0, stream>>>(plan, status_dev); break;
         default: return cudaErrorInvalidValue;
     }
     return cudaGetLastError();

@@ -2,7 +2,8 @@
 
 Field names, types and defaults are those of the reference's ``StagehandConfig``
 (``src/stagehand/config.py:9-46``) so existing construction code keeps working.
-The three trailing fields are additions of this implementation; all are optional.
+The fields after "additions" are this implementation's own; all are optional and default to the
+reference's behaviour.
 """
 from __future__ import annotations
 

@@ -574,10 +574,10 @@ class StagehandScheduler:
         self._streamer = Int8BlockStreamer(device, self._engine.copy_stream, n_staging,
                                            dequant_priority=self._config.dequant_stream_priority)
         pool_kw = dict(on_allocation=getattr(self._budget, "invalidate", None), on_trim=self._view_cache.clear)
-        if getattr(self._config, "device_pool_backend", "torch") == "vmm":
+        if self._config.device_pool_backend == "vmm":
             from stagehand_b200.device_pool import VmmDeviceSlabPool
 
-            self._device_pool = VmmDeviceSlabPool(device, ceiling_mb=int(getattr(self._config, "vmm_ceiling_mb", 0)) or None,
+            self._device_pool = VmmDeviceSlabPool(device, ceiling_mb=int(self._config.vmm_ceiling_mb) or None,
                                                   **pool_kw)
             if hasattr(self._budget, "set_external_bytes_source"):
                 self._budget.set_external_bytes_source(self._device_pool.mapped_bytes)
@@ -597,7 +597,7 @@ class StagehandScheduler:
         self._streamer.ensure_staging(largest, largest_dyn if self._device_sources else 0)
 
     def _image_cache_budget(self) -> int:
-        mb = int(getattr(self._config, "packed_image_cache_mb", -1))
+        mb = int(self._config.packed_image_cache_mb)
         if mb >= 0:
             return mb * 1024 * 1024
         try:
@@ -675,7 +675,7 @@ class StagehandScheduler:
         elif image.static_ready:
             self._telemetry.record_image_cache_hit()
         if not image.static_ready:
-            plan.fill_static(image.buffer, threads=int(getattr(self._config, "pack_threads", 8)))
+            plan.fill_static(image.buffer, threads=int(self._config.pack_threads))
             image.static_ready = True
         if plan.dynamic_rows:
             if image.last_copy is not None and not image.last_copy.done():

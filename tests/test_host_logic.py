@@ -237,3 +237,91 @@ def test_module_backed_block_mode_and_layer_mode_run_on_cpu() -> None:
         out = wrapped(torch.ones(2, 16, dtype=torch.bfloat16))
     assert torch.equal(out, ref) and rt.traced and rt.trace_order == ["0", "2"]
     rt.shutdown()
+
+
+class _BlockCountBudget:
+    """Budget stub: usage = resident or in-flight blocks x 1 MB (the reference's tests drive eviction the same way)."""
+
+    def __init__(self, residency, block_ids, high: int, low: int) -> None:
+        self._res, self._ids = residency, block_ids
+        self.high_watermark_mb, self.low_watermark_mb = high, low
+
+    def vram_used_mb(self) -> float:
+        live = (sh.BlockState.GPU_READY, sh.BlockState.PREFETCHING)
+        return float(sum(self._res.get_state(b) in live for b in self._ids))
+
+    def above_high_watermark(self) -> bool:
+        return self.vram_used_mb() >= self.high_watermark_mb
+
+    def below_low_watermark(self) -> bool:
+        return self.vram_used_mb() < self.low_watermark_mb
+
+    def can_prefetch(self) -> bool:
+        return not self.above_high_watermark()
+
+    def headroom_mb(self) -> float:
+        return self.high_watermark_mb - self.vram_used_mb()
+
+    def invalidate(self) -> None:
+        pass
+
+
+@pytest.mark.parametrize("mode", ["reference", "backward_prefetch", "training_lookahead"])
+def test_training_schedules_on_a_counted_budget(mode: str) -> None:
+    """Forward 0..11 then backward 11..0 with room for about half the blocks, three schedules.
+
+    Every schedule must have each block resident when it is used and leave no reference behind; the
+    look-ahead schedule must not load more blocks per step than the reference's, and must load most of
+    them ahead of use rather than on demand.
+    """
+    n = 12
+    model = nn.Sequential(*[nn.Linear(256, 1024) for _ in range(n)])        # 1 MB of fp32 weights per block
+    for p in model.parameters():
+        p.requires_grad_(False)
+    cfg = sh.StagehandConfig(pinned_pool_mb=16, pinned_slab_mb=2, telemetry_enabled=False, nan_inf_check=False,
+                             prefetch_window_blocks=2, eviction_cooldown_steps=0,
+                             backward_prefetch=mode == "backward_prefetch",
+                             training_lookahead=mode == "training_lookahead")
+    rt = sh.StagehandRuntime(model, cfg, block_pattern=r"^\d+$", dtype=torch.float32, inference_mode=False)
+    sched = rt._scheduler
+    ids = [e.block_id for e in rt._registry.blocks_in_order()]
+    sched._budget = _BlockCountBudget(rt._residency, ids, high=7, low=4)
+    loads = {"demand": 0, "ahead": 0}
+    inner = sched._load_block_to_gpu
+
+    def counted(block_id, speculative=False):
+        if rt._residency.get_state(block_id) is sh.BlockState.UNLOADED:
+            loads["ahead" if speculative else "demand"] += 1
+        return inner(block_id, speculative=speculative)
+
+    sched._load_block_to_gpu = counted
+    per_step = []
+    for step in range(3):
+        before = dict(loads)
+        rt.begin_step(step)
+        for b in ids:
+            sched.before_block(b)
+            assert rt._residency.get_state(b) is sh.BlockState.GPU_READY
+            sched.after_block(b)
+        sched.enter_backward_phase()
+        for b in reversed(ids):
+            sched.before_block(b)
+            assert rt._residency.get_state(b) is sh.BlockState.GPU_READY
+            sched.after_block(b)
+        rt.end_step()
+        assert all(rt._residency.get_entry(b).refcount == 0 for b in ids)
+        assert sched._budget.vram_used_mb() <= 7 + 2           # never far past the high watermark
+        per_step.append({k: loads[k] - before[k] for k in loads})
+    rt.shutdown()
+    steady = per_step[-1]
+    test_training_schedules_on_a_counted_budget.results[mode] = steady
+    if mode == "reference":
+        assert steady["demand"] >= n // 2                       # its backward pass loads on demand
+    if mode == "training_lookahead":
+        ref = test_training_schedules_on_a_counted_budget.results.get("reference")
+        assert steady["demand"] <= 2
+        if ref is not None:
+            assert steady["demand"] + steady["ahead"] <= ref["demand"] + ref["ahead"]
+
+
+test_training_schedules_on_a_counted_budget.results = {}

@@ -53,7 +53,9 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="flux", choices=["flux", "flux_small", "flux_mistral", "kernel_sweep", "video_train", "rotation", "vmm"])
+    ap.add_argument("--workload", default="flux", choices=["flux", "flux_small", "flux_mistral", "kernel_sweep", "video_train", "rotation", "vmm", "flux_bf16"])
+    ap.add_argument("--no-mirror", action="store_true",
+                    help="flux_bf16: the reference's per-parameter copies instead of the page-locked block mirror")
     ap.add_argument("--blocks", type=int, default=0, help="video_train: number of blocks (default 48)")
     ap.add_argument("--tokens", type=int, default=6144, help="video_train: video tokens per step")
     ap.add_argument("--shapes", default="", help="kernel_sweep: comma-separated NxK list (default: the full sweep)")
@@ -568,6 +570,88 @@ def run_video_training(args) -> None:
     print(json.dumps(line), flush=True)
 
 
+def run_module_bf16(args) -> None:
+    """Module-backed bf16 streaming (no quantisation, no file): the Flux-shaped DiT held as CPU parameters.
+
+    With ``pinned_module_mirror`` a block load is one DMA of its page-locked host copy into a pooled slab and an
+    eviction copies nothing back; without it the runtime does what the reference does (a copy per parameter on
+    the compute stream at load, a device-to-host copy per parameter at eviction).
+    """
+    import torch
+
+    import stagehand_b200 as sh
+    from stagehand_b200 import _native as native
+    from stagehand_b200.workloads import BLOCK_PATTERNS, FluxShapedDiT, _SYNTH_WEIGHT_STD
+
+    torch.cuda.set_device(0)
+    K, W = args.steps, max(args.warmup, 0)
+    t_setup = time.perf_counter()
+    link_peak = probe_host_link()
+    model = FluxShapedDiT(n_double=19, n_single=38, hidden=3072, heads=24, dtype=torch.bfloat16)
+    g = torch.Generator().manual_seed(0)
+    by_shape: dict[tuple[int, ...], torch.Tensor] = {}
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            p.requires_grad_(False)
+            if p.dim() == 2:
+                src = by_shape.get(tuple(p.shape))
+                if src is None:
+                    src = by_shape[tuple(p.shape)] = (torch.randn(p.shape, generator=g) * _SYNTH_WEIGHT_STD).to(p.dtype)
+                p.copy_(src)
+            elif name.endswith("bias"):
+                p.zero_()
+            else:
+                p.fill_(1.0)
+    weight_bytes = sum(p.numel() * p.element_size() for p in model.parameters())
+    budget_mb = int(args.vram_budget_gb * 1024)
+    cfg = sh.StagehandConfig(
+        pinned_pool_mb=2048, pinned_slab_mb=1024, vram_high_watermark_mb=int(budget_mb * 0.8),
+        vram_low_watermark_mb=int(budget_mb * 0.6), prefetch_window_blocks=args.prefetch_k, eviction_cooldown_steps=0,
+        nan_inf_check=False, strict_bf16=False, telemetry_enabled=True, telemetry_interval_steps=0,
+        telemetry_file=os.devnull, prefetch_wraparound=not args.no_wraparound, pinned_module_mirror=not args.no_mirror)
+    rt = sh.StagehandRuntime(model, cfg, block_pattern=BLOCK_PATTERNS["flux"], group="dit", dtype=torch.bfloat16,
+                             inference_mode=True)
+    host_inputs = [torch.randn(1, 4096, 3072, generator=g).to(torch.bfloat16).pin_memory(),
+                   torch.randn(1, 512, 3072, generator=g).to(torch.bfloat16).pin_memory(),
+                   torch.randn(1, 3072, generator=g).to(torch.bfloat16).pin_memory()]
+    step = [0]
+
+    def go(n: int) -> None:
+        run_steps(rt, model, host_inputs, None, n, step[0], True, True)
+        step[0] += n
+
+    go(W)
+    torch.cuda.synchronize()
+    setup_s = time.perf_counter() - t_setup
+    native.lib().sh_stats_reset()
+    sampler = ClockSampler(0)
+    ms, clocks = timed_region(go, K, {"world": 1, "rank": 0}, sampler)
+    last = rt.telemetry.last()
+    stats = native.stats()
+    rt.shutdown()
+    ms_step = ms / K
+    value = last.h2d_bytes / (ms_step / 1e3) / 1e9
+    link_gbs = last.link_bytes / (ms_step / 1e3) / 1e9
+    print(json.dumps({
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "flux1-dev-shaped DiT 19 double + 38 single blocks, hidden 3072, 4096+512 tokens, "
+                               "module-backed bf16 parameters (no quantisation, no file)",
+                   "weight_bytes": weight_bytes, "vram_budget_gb": args.vram_budget_gb, "prefetch_k": args.prefetch_k,
+                   "pinned_module_mirror": not args.no_mirror, "prefetch_wraparound": not args.no_wraparound,
+                   "l2": "weights larger than L2; no flush"},
+        "clocks": clocks,
+        "e2e": {"value": value, "unit": UNIT, "ms_per_step": ms_step,
+                "h2d_bytes_per_step": last.link_bytes + sum(t.numel() * t.element_size() for t in host_inputs),
+                "d2h_bytes_per_step": 4,
+                "host_link": {"peak_gbs": link_peak, "achieved_gbs": link_gbs, "frac": link_gbs / link_peak,
+                              "peak_source": "page-locked 4 x 1 GiB cudaMemcpyAsync probe in this run"}},
+        "gpu_launches": stats["kernel_launches"], "roofline": None, "cpu_baseline": None,
+        "telemetry": {"hits": last.prefetch_hits, "misses": last.prefetch_misses, "soft_hits": last.soft_hits,
+                      "evictions": last.evictions, "host_stall_ms": last.stall_time_ms},
+        "setup_s": setup_s}), flush=True)
+
+
 def run_rotation(args) -> None:
     """Slot-rotation engine: forward then backward sweeps over 24 blocks of 256 MiB through a 3-slot window.
 
@@ -679,6 +763,10 @@ def main() -> None:
     if args.workload == "kernel_sweep":
         if int(os.environ.get("RANK", "0")) == 0:
             run_kernel_sweep(args)
+        return
+    if args.workload == "flux_bf16":
+        if int(os.environ.get("RANK", "0")) == 0:
+            run_module_bf16(args)
         return
     if args.workload in ("rotation", "vmm"):      # the engines beside the path: single-GPU measurements
         if int(os.environ.get("RANK", "0")) == 0:

@@ -204,6 +204,7 @@ class StagehandScheduler:
         self._evicted_copies: dict[str, dict[str, torch.Tensor]] = {}   # block -> name -> CPU copy in the runtime dtype
         # Training: trainable parameters (and their gradients) leave an evicted block through page-locked
         # buffers by an asynchronous copy; the event says when the host may read them.
+        self._module_mirrors: dict[str, tuple[torch.Tensor, dict[str, torch.Tensor], bool]] = {}   # flat, views, pinned
         self._save_buffers: dict[tuple[str, str, str], torch.Tensor] = {}
         self._pending_saves: dict[str, torch.cuda.Event] = {}
 
@@ -374,6 +375,15 @@ class StagehandScheduler:
         if self._pending_saves:
             self._await_saves()
         self._save_buffers.clear()       # parameters that still point at a buffer keep it alive themselves
+        if self._module_mirrors:
+            from stagehand_b200 import _native
+
+            if torch.cuda.is_available():
+                torch.cuda.synchronize()          # no DMA may still read a buffer that stops being page-locked
+            for flat, _views, pinned in self._module_mirrors.values():
+                if pinned:
+                    _native.lib().sh_host_unregister(flat.data_ptr())
+            self._module_mirrors.clear()          # the memory stays with the parameters that view it
 
     # ── per-block hooks ──────────────────────────────────────────────
 
@@ -793,11 +803,60 @@ class StagehandScheduler:
             else:
                 region.zero_()
 
+    def _mirror_applies(self, module: nn.Module) -> bool:
+        return bool(self._config.pinned_module_mirror and self._inference_mode and torch.cuda.is_available()
+                    and all(not p.requires_grad and p.device.type != "meta" for p in module.parameters()))
+
+    def _module_mirror(self, block_id: str, entry: "BlockEntry", module: nn.Module, layout: Layout) -> torch.Tensor:
+        """The block's page-locked host copy in the runtime dtype; the module's CPU parameters are views of it.
+
+        Built at the block's first load.  At later loads a parameter that no longer points at its view
+        (the caller assigned new data) is copied in again; an in-place edit of the view is already in the buffer.
+        """
+        from stagehand_b200 import _native
+
+        hit = self._module_mirrors.get(block_id)
+        if hit is None:
+            flat = torch.empty(max(entry.size_bytes, 1), dtype=torch.uint8)
+            pinned = _native.lib().sh_host_register(flat.data_ptr(), flat.numel()) == 0
+            views = {name: flat[off : off + numel * dtype.itemsize].view(dtype).reshape(shape)
+                     for name, shape, dtype, off, numel in layout}
+            hit = (flat, views, pinned)
+            self._module_mirrors[block_id] = hit
+        flat, views, _pinned = hit
+        for name, _shape, dtype, _off, _numel in layout:
+            live = _get_param_data(module, name)
+            view = views[name]
+            if live.data_ptr() != view.data_ptr() or live.dtype != dtype:
+                with torch.inference_mode(False):
+                    view.copy_(live.detach().to(dtype))
+                _set_param_data(module, name, view)
+        return flat
+
+    def _load_module_backed_mirrored(self, block_id: str, entry: "BlockEntry", res: "ResidencyEntry",
+                                     module: nn.Module) -> None:
+        self._ensure_int8_path()
+        layout = _build_param_layout(module, entry.dtype)
+        flat = self._module_mirror(block_id, entry, module, layout)
+        res.param_layout = layout
+        out_slab = self._device_pool.acquire(entry.size_bytes)
+        ticket = self._streamer.submit_plain(block_id, flat.data_ptr(), entry.size_bytes, out_slab)
+        res.device_slab = out_slab
+        res.gpu_tensor = out_slab.tensor[: entry.size_bytes].view(entry.dtype)
+        self._pending_handles[block_id] = ticket
+        for nxt in (BlockState.HOST_STAGED, BlockState.PREFETCHING):
+            self._residency.transition(block_id, nxt)
+        self._telemetry.record_h2d(entry.size_bytes)
+        self._telemetry.record_link(entry.size_bytes)
+
     def _load_module_backed_direct(self, block_id: str, entry: "BlockEntry", res: "ResidencyEntry") -> None:
         """Module-backed block: parameters live on the module; copy them into one flat device tensor."""
         module = entry.module_ref()
         if module is None:
             return   # as in the reference: a collected module is a silent no-op
+        if self._mirror_applies(module):
+            self._load_module_backed_mirrored(block_id, entry, res, module)
+            return
         device = "cuda" if torch.cuda.is_available() else "cpu"
         layout = _build_param_layout(module, entry.dtype)
         res.param_layout = layout
@@ -1018,6 +1077,11 @@ class StagehandScheduler:
                 if saved_async:
                     self._pending_saves[block_id] = torch.cuda.Event()
                     self._pending_saves[block_id].record()
+            elif block_id in self._module_mirrors and self._inference_mode:
+                # frozen parameters of an inference run: their host copy is still current
+                views = self._module_mirrors[block_id][1]
+                for name, _shape, _dtype, _off, _numel in res.param_layout:
+                    _set_param_data(module, name, views[name])
             else:
                 for name, _shape, _dtype, _off, _numel in res.param_layout:
                     _set_param_data(module, name, _get_param_data(module, name).to("cpu").clone())

@@ -210,6 +210,17 @@ class Int8BlockStreamer:
         launches = -(-image.n_descs // _native.MAX_DESCS_PER_LAUNCH)
         return StreamTicket(image.block_id, ready, copied, link_bytes=image.total_bytes, launches=launches)
 
+    def submit_plain(self, block_id: str, host_ptr: int, nbytes: int, out_slab: DeviceSlab) -> StreamTicket:
+        """A block already in the runtime dtype in page-locked memory: one DMA straight into its slab, no kernel."""
+        if out_slab.last_use is not None:
+            out_slab.last_use.block_stream(self.copy_stream)       # previous readers of the slab are done
+            release_event(out_slab.last_use)
+            out_slab.last_use = None
+        _native.check(self._lib.sh_copy_h2d_async(out_slab.tensor.data_ptr(), host_ptr, nbytes,
+                                                  stream_handle(self.copy_stream)), f"sh_copy_h2d_async({block_id})")
+        ready = acquire_event().record(self.copy_stream)
+        return StreamTicket(block_id, ready, None, link_bytes=nbytes, launches=0)
+
     def submit_from_device(self, image: PackedBlockImage, source: DeviceSource, fused: bool,
                            dynamic_host: HostImage | None, out_slab: DeviceSlab) -> StreamTicket:
         """Image whose static section is resident in HBM (this GPU's, or a peer's over NVLink).

@@ -275,3 +275,73 @@ def test_module_owned_parameter_edits_reach_the_next_load(cache_mb: int, tmp_pat
         torch.cuda.synchronize()
         assert torch.equal(seen[-1], expect.to(torch.bfloat16).float()), step
     rt.shutdown()
+
+
+def _module_backed(tmp_path: Path, mirror: bool, **cfg_kw):
+    torch.manual_seed(7)
+    model = TinyBlockModel(n_blocks=4, hidden=256, heads=4, mlp=1024)
+    with torch.no_grad():
+        for p in model.parameters():
+            if p.dim() == 2:
+                p.normal_(0.0, 0.9)
+            p.requires_grad_(False)
+    base = dict(pinned_pool_mb=64, pinned_slab_mb=16, telemetry_enabled=True, telemetry_file=str(tmp_path / "t.jsonl"),
+                nan_inf_check=False, prefetch_window_blocks=2, eviction_cooldown_steps=0, pinned_module_mirror=mirror)
+    base.update(cfg_kw)
+    rt = sh.StagehandRuntime(model, sh.StagehandConfig(**base), block_pattern=BLOCK_PATTERNS["tiny"], group="t",
+                             dtype=torch.bfloat16, inference_mode=True)
+    return model, rt
+
+
+def test_module_backed_blocks_stream_from_a_pinned_mirror(tmp_path: Path) -> None:
+    """Module-backed inference with ``pinned_module_mirror``: same outputs as the reference's copy path, one DMA per
+    load, nothing copied back at eviction, and the module is a working CPU model again after shutdown."""
+    import gc
+
+    x = torch.randn(1, 32, 256, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16)
+    outs = {}
+    for mirror in (False, True):
+        gc.collect()
+        base_mb = int(torch.cuda.memory_allocated() >> 20)
+        model, rt = _module_backed(tmp_path, mirror, vram_high_watermark_mb=base_mb + 4, vram_low_watermark_mb=base_mb + 2)
+        ys = []
+        for step in range(3):
+            rt.begin_step(step)
+            with torch.inference_mode(), rt.managed_forward():
+                ys.append(model(x.cuda()).float().cpu())
+            rt.end_step()
+        last = rt.telemetry.last()
+        assert last.evictions >= 2 and torch.equal(ys[0], ys[2])
+        if mirror:
+            evicted = [e for e in rt._registry.blocks_in_order()
+                       if rt._residency.get_state(e.block_id) is sh.BlockState.UNLOADED]
+            assert evicted
+            for e in evicted:          # parameters are views of the block's one host buffer, in the runtime dtype
+                flat, views, pinned = rt._scheduler._module_mirrors[e.block_id]
+                w = e.module_ref().qkv.weight
+                assert w.device.type == "cpu" and w.dtype == torch.bfloat16 and pinned
+                assert flat.data_ptr() <= w.data_ptr() < flat.data_ptr() + flat.numel()
+            # new data assigned to a parameter between steps is what the next load delivers
+            blk = model.blocks[0]
+            if rt._residency.get_state("blocks.0") is sh.BlockState.UNLOADED:
+                blk.norm1.weight.data = torch.full_like(blk.norm1.weight.data, 2.0)
+                rt.begin_step(3)
+                with torch.inference_mode(), rt.managed_forward():
+                    y_edit = model(x.cuda()).float().cpu()
+                rt.end_step()
+                assert not torch.equal(y_edit, ys[0])
+                blk.norm1.weight.data.fill_(1.0)          # in place on the view: already in the buffer
+                rt.begin_step(4)
+                with torch.inference_mode(), rt.managed_forward():
+                    y_back = model(x.cuda()).float().cpu()
+                rt.end_step()
+                assert torch.equal(y_back, ys[0])
+        rt.shutdown()
+        torch.cuda.synchronize()
+        outs[mirror] = ys[0]
+        if mirror:
+            model.cpu()
+            with torch.no_grad():
+                y_cpu = model(x).float()
+            assert torch.isfinite(y_cpu).all() and (y_cpu - ys[0]).abs().max() <= 0.1 * ys[0].abs().max()
+    assert torch.equal(outs[False], outs[True])

@@ -817,10 +817,11 @@ class StagehandScheduler:
 
         hit = self._module_mirrors.get(block_id)
         if hit is None:
-            flat = torch.empty(max(entry.size_bytes, 1), dtype=torch.uint8)
+            with torch.inference_mode(False):      # ordinary tensors: they outlive the caller's inference scope
+                flat = torch.empty(max(entry.size_bytes, 1), dtype=torch.uint8)
+                views = {name: flat[off : off + numel * dtype.itemsize].view(dtype).reshape(shape)
+                         for name, shape, dtype, off, numel in layout}
             pinned = _native.lib().sh_host_register(flat.data_ptr(), flat.numel()) == 0
-            views = {name: flat[off : off + numel * dtype.itemsize].view(dtype).reshape(shape)
-                     for name, shape, dtype, off, numel in layout}
             hit = (flat, views, pinned)
             self._module_mirrors[block_id] = hit
         flat, views, _pinned = hit

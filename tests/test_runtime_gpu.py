@@ -281,9 +281,13 @@ def _module_backed(tmp_path: Path, mirror: bool, **cfg_kw):
     torch.manual_seed(7)
     model = TinyBlockModel(n_blocks=4, hidden=256, heads=4, mlp=1024)
     with torch.no_grad():
-        for p in model.parameters():
+        for name, p in model.named_parameters():
             if p.dim() == 2:
                 p.normal_(0.0, 0.9)
+            elif name.endswith("bias"):
+                p.zero_()
+            else:
+                p.fill_(1.0)
             p.requires_grad_(False)
     base = dict(pinned_pool_mb=64, pinned_slab_mb=16, telemetry_enabled=True, telemetry_file=str(tmp_path / "t.jsonl"),
                 nan_inf_check=False, prefetch_window_blocks=2, eviction_cooldown_steps=0, pinned_module_mirror=mirror)

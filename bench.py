@@ -55,7 +55,7 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="flux", choices=["flux", "flux_small", "flux_mistral", "kernel_sweep", "video_train", "rotation", "vmm", "flux_bf16"])
     ap.add_argument("--no-mirror", action="store_true",
-                    help="flux_bf16: the reference's per-parameter copies instead of the page-locked block mirror")
+                    help="flux_bf16: the plain per-parameter torch copies instead of the page-locked block mirror")
     ap.add_argument("--blocks", type=int, default=0, help="video_train: number of blocks (default 48)")
     ap.add_argument("--tokens", type=int, default=6144, help="video_train: video tokens per step")
     ap.add_argument("--shapes", default="", help="kernel_sweep: comma-separated NxK list (default: the full sweep)")
@@ -574,8 +574,8 @@ def run_module_bf16(args) -> None:
     """Module-backed bf16 streaming (no quantisation, no file): the Flux-shaped DiT held as CPU parameters.
 
     With ``pinned_module_mirror`` a block load is one DMA of its page-locked host copy into a pooled slab and an
-    eviction copies nothing back; without it the runtime does what the reference does (a copy per parameter on
-    the compute stream at load, a device-to-host copy per parameter at eviction).
+    eviction copies nothing back; without it the runtime takes its plain torch-copy path (a copy per parameter at
+    load, a device-to-host copy per parameter at eviction as the reference's eviction does).
     """
     import torch
 

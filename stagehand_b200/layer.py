@@ -94,7 +94,7 @@ def _first_tensor(output: object) -> torch.Tensor | None:
 class LayerRuntime:
     def __init__(self, model: nn.Module, vram_budget: str | int | None = None, ram_budget: str | int | None = None,
                  prefetch_k: int = 3, dtype: torch.dtype = torch.bfloat16, inference_mode: bool = False,
-                 telemetry: bool = True, pool: PinnedPool | None = None) -> None:
+                 telemetry: bool = True, pool: PinnedPool | None = None, pinned_mirror: bool = False) -> None:
         self._model = model
         self._dtype = dtype
         self._prefetch_k = prefetch_k
@@ -107,6 +107,7 @@ class LayerRuntime:
         self._all_layer_names = [name for name, _ in layers]
         self._config = _auto_pool_config(layers, dtype, prefetch_k, _parse_budget(vram_budget), _parse_budget(ram_budget))
         self._config.telemetry_enabled = telemetry
+        self._config.pinned_module_mirror = bool(pinned_mirror)     # inference only; see StagehandConfig
         self._pool = pool if pool is not None else PinnedPool(total_mb=self._config.pinned_pool_mb,
                                                               slab_mb=self._config.pinned_slab_mb)
         copy_stream = torch.cuda.Stream(priority=self._config.copy_stream_priority) if torch.cuda.is_available() else None
@@ -208,7 +209,9 @@ class LayerRuntime:
         self._record_pool_stats()
         self._scheduler.end_step()
         self._remove_hooks()
+        mirrors = self._scheduler._module_mirrors
         self._build_scheduler([(lid, self._layer_map[lid]) for lid in self._trace_order], self._prefetch_k)
+        self._scheduler._module_mirrors = mirrors       # layer ids are unchanged: the host copies carry over
         self._install_hooks(self._trace_order, traced=True)
         self._step += 1
         self._scheduler.begin_step(self._step)

@@ -349,3 +349,26 @@ def test_module_backed_blocks_stream_from_a_pinned_mirror(tmp_path: Path) -> Non
                 y_cpu = model(x).float()
             assert torch.isfinite(y_cpu).all() and (y_cpu - ys[0]).abs().max() <= 0.1 * ys[0].abs().max()
     assert torch.equal(outs[False], outs[True])
+
+
+def test_layer_mode_with_a_pinned_mirror() -> None:
+    """``stagehand.layer(..., pinned_mirror=True)``: trace pass, rebuilt schedule and later passes all match the plain model."""
+    from torch import nn
+
+    torch.manual_seed(3)
+    model = nn.Sequential(nn.Linear(512, 2048), nn.GELU(), nn.Linear(2048, 2048), nn.GELU(), nn.Linear(2048, 512))
+    model = model.to(torch.bfloat16)
+    x = torch.randn(4, 512, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16)
+    with torch.no_grad():
+        expect = model.cuda()(x.cuda()).float().cpu()
+    model.cpu()
+    wrapped = sh.layer(model, vram_budget="4MB", inference_mode=True, telemetry=False, prefetch_k=1, pinned_mirror=True)
+    rt = wrapped._stagehand_layer_runtime
+    outs = []
+    for _ in range(4):
+        with torch.inference_mode():
+            outs.append(wrapped(x.cuda()).float().cpu())
+    torch.cuda.synchronize()
+    assert all(torch.equal(o, expect) for o in outs)
+    assert rt.traced and len(rt._scheduler._module_mirrors) == 3
+    rt.shutdown()

@@ -71,7 +71,8 @@ class StagehandConfig:
     # Inference, module-backed blocks (no file behind them): keep each block's frozen parameters in one
     # page-locked host buffer in the runtime dtype (the module's CPU parameters become views of it), load a
     # block with one DMA into a pooled VRAM slab on the copy stream, and evict it by pointing the parameters
-    # back at those views -- nothing is copied back.  Off: per-parameter torch copies both ways.
+    # back at those views -- nothing is copied back (so a value the caller writes into the VRAM copy is lost at
+    # eviction; edit the CPU parameter instead).  Off: per-parameter torch copies both ways.
     pinned_module_mirror: bool = False
     # Where the block slabs in VRAM come from: "torch" (caching allocator) or "vmm" (the C++ virtual-memory
     # slab allocator: parked slabs can be unmapped under `vmm_ceiling_mb` without fragmenting anything).

@@ -804,8 +804,10 @@ class StagehandScheduler:
                 region.zero_()
 
     def _mirror_applies(self, module: nn.Module) -> bool:
+        # An inference runtime never trains, so the host copy stays current whatever ``requires_grad`` says;
+        # a value written into the VRAM copy by the caller is not carried back in this mode.
         return bool(self._config.pinned_module_mirror and self._inference_mode and torch.cuda.is_available()
-                    and all(not p.requires_grad and p.device.type != "meta" for p in module.parameters()))
+                    and all(p.device.type != "meta" for p in module.parameters()))
 
     def _module_mirror(self, block_id: str, entry: "BlockEntry", module: nn.Module, layout: Layout) -> torch.Tensor:
         """The block's page-locked host copy in the runtime dtype; the module's CPU parameters are views of it.

@@ -51,12 +51,12 @@ __all__ = [
 
 def layer(model: nn.Module, *, vram_budget: str | int | None = None, ram_budget: str | int | None = None,
           prefetch_k: int = 3, dtype: torch.dtype = torch.bfloat16, inference_mode: bool = False,
-          telemetry: bool = True, pool: PinnedPool | None = None, pinned_mirror: bool = False) -> nn.Module:
+          telemetry: bool = True, pool: PinnedPool | None = None, pinned_mirror: bool = True) -> nn.Module:
     """One-line layer mode: hooks every Linear / Conv2d / Embedding; returns the same model.
 
     The runtime is reachable as ``model._stagehand_layer_runtime``
     (reference ``src/stagehand/__init__.py:621-651``).  *pinned_mirror* (not in the reference; inference
-    only) streams every layer from one page-locked host buffer instead of per-parameter copies.
+    runtimes on a GPU only) streams every layer from one page-locked host buffer instead of per-parameter copies.
     """
     runtime = LayerRuntime(model, vram_budget=vram_budget, ram_budget=ram_budget, prefetch_k=prefetch_k, dtype=dtype,
                            inference_mode=inference_mode, telemetry=telemetry, pool=pool, pinned_mirror=pinned_mirror)

@@ -72,8 +72,9 @@ class StagehandConfig:
     # page-locked host buffer in the runtime dtype (the module's CPU parameters become views of it), load a
     # block with one DMA into a pooled VRAM slab on the copy stream, and evict it by pointing the parameters
     # back at those views -- nothing is copied back (so a value the caller writes into the VRAM copy is lost at
-    # eviction; edit the CPU parameter instead).  Off: per-parameter torch copies both ways.
-    pinned_module_mirror: bool = False
+    # eviction; edit the CPU parameter instead).  Off: per-parameter torch copies both ways.  Training runtimes
+    # and hosts without CUDA always take the copy path.
+    pinned_module_mirror: bool = True
     # Where the block slabs in VRAM come from: "torch" (caching allocator) or "vmm" (the C++ virtual-memory
     # slab allocator: parked slabs can be unmapped under `vmm_ceiling_mb` without fragmenting anything).
     device_pool_backend: str = "torch"

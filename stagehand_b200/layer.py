@@ -94,7 +94,7 @@ def _first_tensor(output: object) -> torch.Tensor | None:
 class LayerRuntime:
     def __init__(self, model: nn.Module, vram_budget: str | int | None = None, ram_budget: str | int | None = None,
                  prefetch_k: int = 3, dtype: torch.dtype = torch.bfloat16, inference_mode: bool = False,
-                 telemetry: bool = True, pool: PinnedPool | None = None, pinned_mirror: bool = False) -> None:
+                 telemetry: bool = True, pool: PinnedPool | None = None, pinned_mirror: bool = True) -> None:
         self._model = model
         self._dtype = dtype
         self._prefetch_k = prefetch_k

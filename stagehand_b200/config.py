@@ -68,12 +68,13 @@ class StagehandConfig:
     # (up, then down again): prefetch the next blocks that are not resident however far ahead they are,
     # evict the block whose next use is farthest away.  Includes backward_prefetch.
     training_lookahead: bool = False
-    # Inference, module-backed blocks (no file behind them): keep each block's frozen parameters in one
+    # Module-backed blocks (no file behind them): keep each block's parameters in one
     # page-locked host buffer in the runtime dtype (the module's CPU parameters become views of it), load a
     # block with one DMA into a pooled VRAM slab on the copy stream, and evict it by pointing the parameters
     # back at those views -- nothing is copied back (so a value the caller writes into the VRAM copy is lost at
-    # eviction; edit the CPU parameter instead).  Off: per-parameter torch copies both ways.  Training runtimes
-    # and hosts without CUDA always take the copy path.
+    # eviction; edit the CPU parameter instead).  Off: per-parameter torch copies both ways.  In a training runtime
+    # only parameters that require gradients (and the gradients) are copied back, asynchronously.  Hosts without
+    # CUDA always take the copy path.
     pinned_module_mirror: bool = True
     # Where the block slabs in VRAM come from: "torch" (caching allocator) or "vmm" (the C++ virtual-memory
     # slab allocator: parked slabs can be unmapped under `vmm_ceiling_mb` without fragmenting anything).

@@ -804,9 +804,10 @@ class StagehandScheduler:
                 region.zero_()
 
     def _mirror_applies(self, module: nn.Module) -> bool:
-        # An inference runtime never trains, so the host copy stays current whatever ``requires_grad`` says;
-        # a value written into the VRAM copy by the caller is not carried back in this mode.
-        return bool(self._config.pinned_module_mirror and self._inference_mode and torch.cuda.is_available()
+        # The host copy of a parameter nothing trains stays current: an inference runtime never trains, and in a
+        # training runtime only parameters that require gradients are written back at eviction.  A value the
+        # caller writes into the VRAM copy of any other parameter is not carried back.
+        return bool(self._config.pinned_module_mirror and torch.cuda.is_available()
                     and all(p.device.type != "meta" for p in module.parameters()))
 
     def _module_mirror(self, block_id: str, entry: "BlockEntry", module: nn.Module, layout: Layout) -> torch.Tensor:
@@ -1080,11 +1081,28 @@ class StagehandScheduler:
                 if saved_async:
                     self._pending_saves[block_id] = torch.cuda.Event()
                     self._pending_saves[block_id].record()
-            elif block_id in self._module_mirrors and self._inference_mode:
-                # frozen parameters of an inference run: their host copy is still current
+            elif block_id in self._module_mirrors:
+                # Parameters nothing trains: their host copy is still current.  Trainable ones are written back
+                # into their own region of the block's page-locked buffer, without waiting for the copy.
                 views = self._module_mirrors[block_id][1]
+                trainable = set() if self._inference_mode else {n for n, p in module.named_parameters() if p.requires_grad}
+                wrote = False
                 for name, _shape, _dtype, _off, _numel in res.param_layout:
+                    if name in trainable:
+                        live = _get_param_data(module, name)
+                        if live.device.type == "cuda":
+                            with torch.inference_mode(False):
+                                views[name].copy_(live.detach(), non_blocking=True)
+                            wrote = True
                     _set_param_data(module, name, views[name])
+                if save_back:
+                    for name, param in module.named_parameters():
+                        if param.grad is not None and param.grad.device.type != "cpu":
+                            param.grad = self._save_async(block_id, name, "grad", param.grad)
+                            wrote = True
+                if wrote:
+                    self._pending_saves[block_id] = torch.cuda.Event()
+                    self._pending_saves[block_id].record()
             else:
                 for name, _shape, _dtype, _off, _numel in res.param_layout:
                     _set_param_data(module, name, _get_param_data(module, name).to("cpu").clone())

@@ -305,3 +305,48 @@ def test_gpu_backward_pass_prefetches_downwards(tmp_path: Path) -> None:
     for mode in (True, "lookahead"):
         for a, b in zip(grads[False], grads[mode]):
             assert torch.equal(a, b)          # the same arithmetic whatever the schedule
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("mirror", [False, True])
+def test_gpu_module_backed_training(mirror: bool, tmp_path: Path) -> None:
+    """No file behind the blocks: frozen weights and trainable adapters both live on the module.
+
+    With the page-locked mirror only the adapters (and their gradients) travel back at eviction; losses and
+    adapter gradients follow a resident twin through four optimiser steps either way.
+    """
+    _streamed, twin = _video_pair(tmp_path)
+    import copy
+
+    model = copy.deepcopy(twin)
+    for (_n, a), (_m, b) in zip(model.named_parameters(), twin.named_parameters()):
+        a.requires_grad_(b.requires_grad)
+    cfg = sh.StagehandConfig(pinned_pool_mb=8, pinned_slab_mb=1, telemetry_enabled=True, nan_inf_check=False,
+                             telemetry_file=str(tmp_path / "t.jsonl"), prefetch_window_blocks=2, backward_prefetch=True,
+                             vram_high_watermark_mb=1, vram_low_watermark_mb=0, eviction_cooldown_steps=0,
+                             pinned_module_mirror=mirror)
+    rt = sh.StagehandRuntime(model, cfg, block_pattern=r"^blocks\.\d+$", dtype=torch.float32, inference_mode=False)
+    g = torch.Generator().manual_seed(4)
+    x, ctx = torch.randn(2, 12, 64, generator=g), torch.randn(2, 5, 64, generator=g)
+    for step in range(4):
+        rt.begin_step(step)
+        with rt.managed_forward(), rt.managed_backward():
+            loss = model(x.cuda().requires_grad_(True), ctx.cuda()).pow(2).mean()
+            loss.backward()
+        rt.end_step()
+        twin.zero_grad()
+        ref_loss = twin(x.clone().requires_grad_(True), ctx).pow(2).mean()
+        ref_loss.backward()
+        assert abs(float(loss.detach()) - float(ref_loss.detach())) < 1e-4 * max(1.0, abs(float(ref_loss.detach())))
+        with torch.no_grad():
+            for (name, got), (_n, ref) in zip(model.named_parameters(), twin.named_parameters()):
+                if "lora" in name:
+                    assert got.grad is not None, name
+                    assert torch.allclose(got.grad.cpu(), ref.grad, atol=1e-5, rtol=1e-3), name
+                    got.add_(got.grad.to(got.device), alpha=-0.5)
+                    ref.add_(ref.grad, alpha=-0.5)
+        model.zero_grad()
+        assert all(rt._residency.get_entry(e.block_id).refcount == 0 for e in rt._registry.blocks_in_order())
+        assert rt.telemetry.last().evictions >= 4
+    assert (len(rt._scheduler._module_mirrors) == 4) == mirror
+    rt.shutdown()

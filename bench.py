@@ -66,6 +66,8 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--no-fused", action="store_true", help="multi-GPU: copy-engine pull + kernel instead of the fused kernel")
     ap.add_argument("--no-wraparound", action="store_true",
                     help="stop the prefetch window at the last block, as the reference does (each step then starts cold)")
+    ap.add_argument("--module-backed", action="store_true",
+                    help="video_train: no checkpoint files; the frozen weights live on the module as CPU parameters")
     ap.add_argument("--training-lookahead", action="store_true",
                     help="video_train: plan prefetch and eviction against the up-then-down order of a training step")
     ap.add_argument("--no-backward-prefetch", action="store_true",
@@ -480,7 +482,23 @@ def run_video_training(args) -> None:
         model.init_adapters(seed=0, std=0.02)
         for name, p in model.named_parameters():
             p.requires_grad_("lora" in name)
-        info = write_sharded_safetensors(model, tmp / "ckpt", blocks_per_shard=4, seed=0, share_values=True)
+        if args.module_backed:
+            # the frozen weights as ordinary CPU parameters (one random draw per shape, copied into every layer)
+            from torch import nn
+
+            g0 = torch.Generator().manual_seed(0)
+            drawn: dict[tuple[int, ...], torch.Tensor] = {}
+            total = 0
+            for module in model.modules():
+                if isinstance(module, nn.Linear) and module.weight.device.type == "meta":
+                    shape = tuple(module.weight.shape)
+                    if shape not in drawn:
+                        drawn[shape] = (torch.randn(shape, generator=g0) * 0.02).to(torch.bfloat16)
+                    module.weight = nn.Parameter(drawn[shape].clone(), requires_grad=False)
+                    total += module.weight.numel() * 2
+            info = {"bytes": total}
+        else:
+            info = write_sharded_safetensors(model, tmp / "ckpt", blocks_per_shard=4, seed=0, share_values=True)
         budget_mb = int(budget_gb * 1024)
         cfg = sh.StagehandConfig(
             pinned_pool_mb=2048, pinned_slab_mb=1024,
@@ -490,7 +508,7 @@ def run_video_training(args) -> None:
             backward_prefetch=not args.no_backward_prefetch, training_lookahead=args.training_lookahead)
         rt = sh.StagehandRuntime(model, cfg, block_pattern=BLOCK_PATTERNS["video"], group="dit", dtype=torch.bfloat16,
                                  inference_mode=False)
-        converted = rt.convert_registry_to_file_backed_sharded(str(tmp / "ckpt"))
+        converted = 0 if args.module_backed else rt.convert_registry_to_file_backed_sharded(str(tmp / "ckpt"))
         g = torch.Generator().manual_seed(0)
         x_host = torch.randn(1, args.tokens, hidden, generator=g).to(torch.bfloat16).pin_memory()
         c_host = torch.randn(1, 512, hidden, generator=g).to(torch.bfloat16).pin_memory()
@@ -552,7 +570,8 @@ def run_video_training(args) -> None:
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": ms_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"video-DiT-shaped {built} blocks (of {n_blocks} asked), hidden {hidden}, {heads} heads, "
-                                   f"FFN {ffn}, self + cross attention, bf16 weights from sharded safetensors, "
+                                   f"FFN {ffn}, self + cross attention, bf16 weights "
+                                   f"{'held by the module (no file)' if args.module_backed else 'from sharded safetensors'}, "
                                    f"{args.tokens}+512 tokens, forward + backward, rank-{rank_r} adapters, checkpointed blocks",
                        "frozen_weights": info["bytes"] // 2, "converted_params": converted,
                        "vram_budget_gb": budget_gb, "prefetch_k": args.prefetch_k,

@@ -15,7 +15,11 @@ the compute stream wait on the block's ready event instead of blocking the host.
 There is no CPU fallback for that path: without CUDA and the native library a
 SquareQ load raises :class:`TransferError`.
 
-Module-backed and safetensors-backed blocks keep the reference's torch-copy paths.
+On a GPU, safetensors-backed blocks take the same packed-image path (their rows are plain copies), and
+module-backed blocks stream from one page-locked host buffer per block with a single DMA
+(``pinned_module_mirror``).  On a host without CUDA both keep the reference's torch-copy paths.
+Opt-in schedule extensions: ``prefetch_wraparound`` (inference), ``backward_prefetch`` and
+``training_lookahead`` (training); all default to the reference's window.
 """
 from __future__ import annotations
 

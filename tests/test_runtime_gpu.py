@@ -372,3 +372,68 @@ def test_layer_mode_with_a_pinned_mirror() -> None:
     assert all(torch.equal(o, expect) for o in outs)
     assert rt.traced and len(rt._scheduler._module_mirrors) == 3
     rt.shutdown()
+
+
+def test_adapter_training_over_a_squareq_base(tmp_path: Path) -> None:
+    """Forward + backward with trainable adapters over INT8 SquareQ base weights, blocks evicted and reloaded.
+
+    The twin holds the same base weights dequantised on the host (``(q - 0) * scale`` in fp32) and stays
+    resident; losses and adapter gradients must agree over three optimiser steps.
+    """
+    import copy
+
+    from stagehand_b200.workloads import VideoShapedDiT
+
+    kw = dict(n_blocks=4, hidden=64, heads=4, ffn=128, rank=4, dtype=torch.float32)
+    model = VideoShapedDiT(**kw)
+    model.init_adapters(seed=5, std=0.05)
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            if p.dim() == 1:
+                p.fill_(1.0)
+    for name, p in model.named_parameters():
+        p.requires_grad_("lora" in name)
+    fpk = tmp_path / "base.fpk"
+    info = write_squareq_fpk(model, r"^blocks\.\d+$", fpk, seed=3)
+    assert info["layers"] == 4 * 10
+    payload = torch.load(str(fpk), weights_only=True)
+    twin = copy.deepcopy(model)
+    with torch.no_grad():
+        for lname, layer in payload["layers"].items():
+            target = twin.get_submodule(lname)
+            out_f, in_f = target.weight.shape
+            q = layer["qweight"][:out_f, :in_f].float()
+            target.weight.copy_((q - layer["zero_point"].float()[:out_f, None]) * layer["scale"].float()[:out_f, None])
+    twin = twin.cuda()                  # the same GPU arithmetic on both sides: only the streaming differs
+    for (_n, a), (_m, b) in zip(twin.named_parameters(), model.named_parameters()):
+        a.requires_grad_(b.requires_grad)
+    cfg = sh.StagehandConfig(pinned_pool_mb=8, pinned_slab_mb=1, telemetry_enabled=True, nan_inf_check=False,
+                             telemetry_file=str(tmp_path / "t.jsonl"), prefetch_window_blocks=2, backward_prefetch=True,
+                             vram_high_watermark_mb=1, vram_low_watermark_mb=0, eviction_cooldown_steps=0)
+    rt = sh.StagehandRuntime(model, cfg, block_pattern=r"^blocks\.\d+$", dtype=torch.float32, inference_mode=False)
+    assert rt.convert_registry_to_file_backed(str(fpk)) == 4 * 10
+    g = torch.Generator().manual_seed(4)
+    x, ctx = torch.randn(2, 12, 64, generator=g) * 0.05, torch.randn(2, 5, 64, generator=g) * 0.05
+    for step in range(3):
+        rt.begin_step(step)
+        with rt.managed_forward(), rt.managed_backward():
+            loss = model(x.cuda().requires_grad_(True), ctx.cuda()).pow(2).mean()
+            loss.backward()
+        rt.end_step()
+        twin.zero_grad()
+        ref_loss = twin(x.cuda().requires_grad_(True), ctx.cuda()).pow(2).mean()
+        ref_loss.backward()
+        assert abs(float(loss.detach()) - float(ref_loss.detach())) <= 1e-5 * abs(float(ref_loss.detach())) + 1e-7
+        with torch.no_grad():
+            for (name, got), (_n, ref) in zip(model.named_parameters(), twin.named_parameters()):
+                if "lora" in name:
+                    assert got.grad is not None, name
+                    scale = float(ref.grad.abs().max()) + 1e-12
+                    assert float((got.grad.cpu() - ref.grad.cpu()).abs().max()) <= 1e-4 * scale, name
+                    got.add_(got.grad.to(got.device), alpha=-0.01)
+                    ref.add_(ref.grad, alpha=-0.01)
+        model.zero_grad()
+        last = rt.telemetry.last()
+        assert last.evictions >= 4 and last.dequant_launches >= 8         # forward and backward both reload
+    assert rt._scheduler._streamer.read_status() == 0
+    rt.shutdown()

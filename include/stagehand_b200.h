@@ -277,10 +277,20 @@ int32_t sh_profile_collect(double* kernel_ms_out, int64_t* launches_out, int64_t
  *   sh_turbo_block_state          block_location / block_slot         engine.rs:375-394 (slot -1 = none)
  *   sh_turbo_counts               num_blocks / num_gpu_slots / num_free_slots   engine.rs:380-382
  *   sh_turbo_drain                drain()                             lib.rs:107-118
+ *
+ * sh_turbo_register_int8_block has no counterpart there (the reference's engine moves bf16 bytes only):
+ * it registers a block as a packed SquareQ INT8 image (*packed_bytes*, what sh_pack_rows and the Python
+ * planner produce) with the descriptors that expand it.  Such a block occupies parameter position 0 of
+ * its slot (*out_bytes* of the runtime dtype); sh_turbo_stage_block takes one pointer, the image; a
+ * step copies the image over the link into a staging buffer the engine owns (one per slot) and runs the
+ * block kernel into the slot; eviction copies nothing back.  sh_turbo_ptr(block, 0, on_gpu = 0) is the
+ * host image.
  */
 int32_t sh_turbo_create(uint64_t* engine_out);
 int32_t sh_turbo_destroy(uint64_t engine);
 int32_t sh_turbo_register_block(uint64_t engine, const uint64_t* param_sizes, int32_t n_params, int32_t* block_out);
+int32_t sh_turbo_register_int8_block(uint64_t engine, const ShParamDesc* descs, int32_t n_descs, uint64_t packed_bytes,
+                                     uint64_t out_bytes, int32_t out_dtype, int32_t* block_out);
 int32_t sh_turbo_initialize(uint64_t engine, int32_t device, int32_t window_size);
 int32_t sh_turbo_stage_block(uint64_t engine, int32_t block, const uint64_t* src_ptrs, int32_t n_ptrs);
 int32_t sh_turbo_set_slot_gpu_ptrs(uint64_t engine, int32_t slot, const uint64_t* ptrs, int32_t n_ptrs);

@@ -103,6 +103,8 @@ _SIGNATURES: dict[str, list] = {
     "sh_turbo_create": [POINTER(c_uint64)],
     "sh_turbo_destroy": [c_uint64],
     "sh_turbo_register_block": [c_uint64, POINTER(c_uint64), c_int32, POINTER(c_int32)],
+    "sh_turbo_register_int8_block": [c_uint64, POINTER(ShParamDesc), c_int32, c_uint64, c_uint64, c_int32,
+                                     POINTER(c_int32)],
     "sh_turbo_initialize": [c_uint64, c_int32, c_int32],
     "sh_turbo_stage_block": [c_uint64, c_int32, POINTER(c_uint64), c_int32],
     "sh_turbo_set_slot_gpu_ptrs": [c_uint64, c_int32, POINTER(c_uint64), c_int32],

@@ -39,6 +39,12 @@ struct Block {
     Location location = kCpu;
     int slot = -1;
     cudaEvent_t moved = nullptr;            // last H2D or D2H of this block
+    // INT8 block: `host` holds the packed image (packed_bytes); on the GPU it occupies parameter position 0
+    // of its slot (out_bytes, the expanded slab) and is never written back -- the image is the source.
+    bool int8 = false;
+    std::vector<ShParamDesc> descs;
+    size_t packed_bytes = 0, out_bytes = 0;
+    int out_dtype = 0;
 };
 
 struct Slot {
@@ -53,6 +59,8 @@ struct Engine {
     std::vector<int> free_slots;
     cudaStream_t prefetch = nullptr, evict = nullptr;
     cudaEvent_t fence = nullptr;            // orders the evict stream after the caller's work
+    std::vector<void*> staging;             // per slot: where a packed INT8 image lands before it is expanded
+    size_t staging_bytes = 0;
     int device = 0;
     bool initialized = false;
 };
@@ -115,7 +123,23 @@ int async_prefetch(Engine& e, int block, int timeout_ms) {
         e.slots[static_cast<size_t>(b.slot)].block = block;
     }
     Slot& s = e.slots[static_cast<size_t>(b.slot)];
-    for (size_t i = 0; i < b.sizes.size(); ++i) {
+    if (b.int8) {
+        // packed image over the link (1 byte per weight), then the block kernel expands it into the slot
+        if (s.ptrs[0] == nullptr) return tfail(SH_ERR_INVALID_ARG, "slot %d has no GPU pointer for parameter 0", b.slot);
+        void* stage = e.staging[static_cast<size_t>(b.slot)];
+        int rc = cuda_check(cudaMemcpyAsync(stage, b.host, b.packed_bytes, cudaMemcpyHostToDevice, e.prefetch),
+                            "cudaMemcpyAsync H2D");
+        if (rc != SH_OK) return rc;
+        rc = sh_dequant_block_async(b.descs.data(), static_cast<int32_t>(b.descs.size()), stage, b.packed_bytes, s.ptrs[0],
+                                    b.out_bytes, b.out_dtype, static_cast<uint64_t>(reinterpret_cast<uintptr_t>(e.prefetch)),
+                                    nullptr);
+        if (rc != SH_OK) {
+            char why[200];
+            sh_last_error(why, sizeof(why));
+            return tfail(rc, "block kernel: %s", why);
+        }
+    }
+    for (size_t i = 0; i < b.sizes.size() && !b.int8; ++i) {
         if (b.sizes[i] == 0) continue;
         if (s.ptrs[i] == nullptr) return tfail(SH_ERR_INVALID_ARG, "slot %d has no GPU pointer for parameter %zu", b.slot, i);
         const int rc = cuda_check(cudaMemcpyAsync(s.ptrs[i], b.host + b.offsets[i], b.sizes[i], cudaMemcpyHostToDevice, e.prefetch),
@@ -133,6 +157,16 @@ int async_evict(Engine& e, int block, uint64_t caller_stream) {
     Block& b = e.blocks[static_cast<size_t>(block)];
     if (b.location == kCpu || b.location == kD2H || b.slot < 0) return SH_OK;
     Slot& s = e.slots[static_cast<size_t>(b.slot)];
+    if (b.int8) {
+        // nothing to write back: the slot is free once everything the caller has queued so far has run
+        cudaStream_t caller = reinterpret_cast<cudaStream_t>(static_cast<uintptr_t>(caller_stream));
+        int rc = SH_OK;
+        if (b.location == kH2D && (rc = cuda_check(cudaStreamWaitEvent(caller, b.moved, 0), "cudaStreamWaitEvent")) != SH_OK)
+            return rc;
+        if ((rc = cuda_check(cudaEventRecord(b.moved, caller), "cudaEventRecord")) != SH_OK) return rc;
+        b.location = kD2H;
+        return SH_OK;
+    }
     // the write-back starts only after everything the caller has queued so far (its use of the block)
     int rc = cuda_check(cudaEventRecord(e.fence, reinterpret_cast<cudaStream_t>(static_cast<uintptr_t>(caller_stream))),
                         "cudaEventRecord");
@@ -202,6 +236,8 @@ int32_t sh_turbo_destroy(uint64_t engine) {
             if (b.host != nullptr) cudaFreeHost(b.host);
             if (b.moved != nullptr) cudaEventDestroy(b.moved);
         }
+        for (void* p : e->staging)
+            if (p != nullptr) cudaFree(p);
         cudaEventDestroy(e->fence);
         cudaStreamDestroy(e->prefetch);
         cudaStreamDestroy(e->evict);
@@ -221,6 +257,28 @@ int32_t sh_turbo_register_block(uint64_t engine, const uint64_t* param_sizes, in
         b.sizes.push_back(static_cast<size_t>(param_sizes[i]));
         b.total += (static_cast<size_t>(param_sizes[i]) + 255) / 256 * 256;
     }
+    e->blocks.push_back(std::move(b));
+    *block_out = static_cast<int32_t>(e->blocks.size() - 1);
+    return SH_OK;
+}
+
+int32_t sh_turbo_register_int8_block(uint64_t engine, const ShParamDesc* descs, int32_t n_descs, uint64_t packed_bytes,
+                                     uint64_t out_bytes, int32_t out_dtype, int32_t* block_out) {
+    Engine* e = as_engine(engine);
+    if (e == nullptr || block_out == nullptr || descs == nullptr || n_descs < 1 || packed_bytes == 0 || out_bytes == 0)
+        return tfail(SH_ERR_INVALID_ARG, "bad register_int8_block arguments");
+    if (out_dtype != SH_DT_BF16 && out_dtype != SH_DT_F16 && out_dtype != SH_DT_F32)
+        return tfail(SH_ERR_INVALID_ARG, "unknown out_dtype %d", out_dtype);
+    if (e->initialized) return tfail(SH_ERR_INVALID_ARG, "blocks must be registered before initialize");
+    Block b;
+    b.int8 = true;
+    b.descs.assign(descs, descs + n_descs);
+    b.packed_bytes = static_cast<size_t>(packed_bytes);
+    b.out_bytes = static_cast<size_t>(out_bytes);
+    b.out_dtype = out_dtype;
+    b.offsets.push_back(0);
+    b.sizes.push_back(b.out_bytes);                       // what it needs of a slot
+    b.total = (b.packed_bytes + 255) / 256 * 256;         // what it needs of page-locked host memory
     e->blocks.push_back(std::move(b));
     *block_out = static_cast<int32_t>(e->blocks.size() - 1);
     return SH_OK;
@@ -250,7 +308,12 @@ int32_t sh_turbo_initialize(uint64_t engine, int32_t device, int32_t window_size
             return rc;
     }
     const int window = std::min<int>(window_size, static_cast<int>(e->blocks.size()));
+    for (const Block& b : e->blocks)
+        if (b.int8) e->staging_bytes = std::max(e->staging_bytes, b.total);
     for (int s = 0; s < window; ++s) {
+        void* stage = nullptr;
+        if (e->staging_bytes != 0 && (rc = cuda_check(cudaMalloc(&stage, e->staging_bytes), "cudaMalloc")) != SH_OK) return rc;
+        e->staging.push_back(stage);
         Slot slot;
         slot.ptrs.assign(max_params, nullptr);
         slot.sizes = capacity;
@@ -267,6 +330,10 @@ int32_t sh_turbo_stage_block(uint64_t engine, int32_t block, const uint64_t* src
         return tfail(SH_ERR_INVALID_ARG, "bad stage_block arguments");
     Block& b = e->blocks[static_cast<size_t>(block)];
     if (n_ptrs != static_cast<int>(b.sizes.size())) return tfail(SH_ERR_INVALID_ARG, "Expected %zu ptrs, got %d", b.sizes.size(), n_ptrs);
+    if (b.int8) {                                          // the one pointer is the packed image
+        memcpy(b.host, reinterpret_cast<const void*>(static_cast<uintptr_t>(src_ptrs[0])), b.packed_bytes);
+        return SH_OK;
+    }
     for (size_t i = 0; i < b.sizes.size(); ++i)
         if (b.sizes[i] != 0) memcpy(b.host + b.offsets[i], reinterpret_cast<const void*>(static_cast<uintptr_t>(src_ptrs[i])), b.sizes[i]);
     return SH_OK;

@@ -56,6 +56,18 @@ class TransferEngine:
                "register_block")
         return int(out.value)
 
+    def register_int8_block(self, descs, n_descs: int, packed_bytes: int, out_bytes: int, out_dtype: int) -> int:
+        """A block kept as a packed SquareQ INT8 image and expanded by the block kernel when it enters a slot.
+
+        *descs* is a ctypes array of ``ShParamDesc`` (``_native.make_descs``), *out_dtype* an ``SH_DT_*`` code.
+        The block uses parameter position 0 of its slot (*out_bytes*); ``stage_block`` takes the image pointer.
+        Not part of the reference's engine, which moves bf16 bytes only.
+        """
+        out = ctypes.c_int32(0)
+        _check(self._lib.sh_turbo_register_int8_block(self._handle, descs, int(n_descs), int(packed_bytes), int(out_bytes),
+                                                      int(out_dtype), ctypes.byref(out)), "register_int8_block")
+        return int(out.value)
+
     def initialize(self, device: int, window_size: int) -> None:
         _check(self._lib.sh_turbo_initialize(self._handle, int(device), int(window_size)), "initialize")
 

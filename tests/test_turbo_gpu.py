@@ -84,3 +84,70 @@ def test_eviction_writes_device_side_changes_back() -> None:
         engine.drain()
     finally:
         engine.close()
+
+
+def test_int8_blocks_are_expanded_into_their_slot() -> None:
+    """Blocks registered as packed SquareQ INT8 images: each step delivers the oracle's bf16 bytes into the slot,
+    forward and backward sweeps, with bf16 blocks of the reference's kind rotating through the same window."""
+    import numpy as np
+
+    from kernel_utils import DT_CODE, HandImage, align
+    from oracle import squareq_oracle as oracle
+    from stagehand_b200 import _native
+
+    rng = np.random.default_rng(21)
+    engine = TransferEngine()
+    images, expected = [], []
+    n_int8 = 4
+    for b in range(n_int8):
+        img = HandImage()
+        parts = []
+        for rows, cols, with_zp in ((96 + 32 * b, 512, False), (64, 1024 + 256 * b, b % 2 == 1)):
+            q = rng.integers(-128, 128, size=(rows, cols), dtype=np.int8)
+            scale = np.exp(rng.standard_normal(rows) * 0.5 - 4.0).astype(np.float32)
+            zp = rng.standard_normal(rows).astype(np.float32) if with_zp else None
+            off = img.add_dequant(q, scale, zp, rows, cols, "bf16")
+            parts.append((off, oracle.dequant_rows(q, scale, zp, rows, cols, "bf16")))
+        host = torch.from_numpy(img.host_bytes())
+        out_bytes = align(img.dst_cursor, 256)
+        idx = engine.register_int8_block(_native.make_descs(img.descs), len(img.descs), host.numel(), out_bytes,
+                                         DT_CODE["bf16"])
+        assert idx == b
+        images.append((host, out_bytes))
+        expected.append(parts)
+    plain = torch.arange(4096, dtype=torch.uint8).repeat(4)               # one ordinary block among them
+    plain_idx = engine.register_block([plain.numel()])
+    engine.initialize(torch.cuda.current_device(), 3)
+    for b, (host, _n) in enumerate(images):
+        engine.stage_block(b, [host.data_ptr()])
+    engine.stage_block(plain_idx, [plain.data_ptr()])
+    capacity = max(max(n for _h, n in images), plain.numel())
+    slots = [torch.full((capacity,), 0xEE, dtype=torch.uint8, device="cuda") for _ in range(engine.num_gpu_slots())]
+    for i, t in enumerate(slots):
+        engine.set_slot_gpu_ptrs(i, [t.data_ptr()])
+
+    def check(block: int) -> None:
+        torch.cuda.current_stream().synchronize()
+        slot = engine.block_slot(block)
+        assert slot is not None and engine.block_location(block) == "gpu"
+        got = slots[slot].cpu().numpy()
+        if block == plain_idx:
+            assert np.array_equal(got[: plain.numel()], plain.numpy())
+            return
+        for off, ref in expected[block]:
+            raw = np.ascontiguousarray(ref).view(np.uint8).reshape(-1)
+            assert np.array_equal(got[off : off + raw.size], raw), block
+
+    order = list(range(n_int8)) + [plain_idx]
+    for _sweep in range(2):
+        for b in order:
+            engine.step(b, "forward")
+            check(b)
+        for b in reversed(order):
+            engine.step(b, "backward")
+            check(b)
+    engine.drain()
+    for b in order:
+        engine.evict_sync(b)
+    assert all(engine.block_location(b) == "cpu" for b in order) and engine.num_free_slots() == 3
+    engine.close()

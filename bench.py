@@ -54,6 +54,8 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="flux", choices=["flux", "flux_small", "flux_mistral", "kernel_sweep", "video_train", "rotation", "vmm", "flux_bf16"])
+    ap.add_argument("--layer-mode", action="store_true",
+                    help="flux_bf16: the one-line API, stagehand.layer(model, ...): every Linear is its own unit")
     ap.add_argument("--no-mirror", action="store_true",
                     help="flux_bf16: the plain per-parameter torch copies instead of the page-locked block mirror")
     ap.add_argument("--blocks", type=int, default=0, help="video_train: number of blocks (default 48)")
@@ -630,16 +632,31 @@ def run_module_bf16(args) -> None:
         vram_low_watermark_mb=int(budget_mb * 0.6), prefetch_window_blocks=args.prefetch_k, eviction_cooldown_steps=0,
         nan_inf_check=False, strict_bf16=False, telemetry_enabled=True, telemetry_interval_steps=0,
         telemetry_file=os.devnull, prefetch_wraparound=not args.no_wraparound, pinned_module_mirror=not args.no_mirror)
-    rt = sh.StagehandRuntime(model, cfg, block_pattern=BLOCK_PATTERNS["flux"], group="dit", dtype=torch.bfloat16,
-                             inference_mode=True)
     host_inputs = [torch.randn(1, 4096, 3072, generator=g).to(torch.bfloat16).pin_memory(),
                    torch.randn(1, 512, 3072, generator=g).to(torch.bfloat16).pin_memory(),
                    torch.randn(1, 3072, generator=g).to(torch.bfloat16).pin_memory()]
     step = [0]
+    if args.layer_mode:
+        # layer mode: the runtime traces the first forward, then schedules; a new forward is a new step
+        sh.layer(model, vram_budget=f"{int(args.vram_budget_gb * 1024)}MB", prefetch_k=args.prefetch_k,
+                 dtype=torch.bfloat16, inference_mode=True, telemetry=True, pinned_mirror=not args.no_mirror)
+        rt = model._stagehand_layer_runtime
+        out_host = torch.empty(1, dtype=torch.float32).pin_memory()
 
-    def go(n: int) -> None:
-        run_steps(rt, model, host_inputs, None, n, step[0], True, True)
-        step[0] += n
+        def go(n: int) -> None:
+            for _ in range(n):
+                inputs = [t.cuda(non_blocking=True) for t in host_inputs]
+                with torch.inference_mode():
+                    y = model(*inputs)
+                out_host.copy_(y.float().abs().mean().reshape(1), non_blocking=True)
+            step[0] += n
+    else:
+        rt = sh.StagehandRuntime(model, cfg, block_pattern=BLOCK_PATTERNS["flux"], group="dit", dtype=torch.bfloat16,
+                                 inference_mode=True)
+
+        def go(n: int) -> None:
+            run_steps(rt, model, host_inputs, None, n, step[0], True, True)
+            step[0] += n
 
     go(W)
     torch.cuda.synchronize()
@@ -657,7 +674,8 @@ def run_module_bf16(args) -> None:
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": "flux1-dev-shaped DiT 19 double + 38 single blocks, hidden 3072, 4096+512 tokens, "
-                               "module-backed bf16 parameters (no quantisation, no file)",
+                               "module-backed bf16 parameters (no quantisation, no file)"
+                               + (", layer mode (stagehand.layer): every Linear its own unit" if args.layer_mode else ""),
                    "weight_bytes": weight_bytes, "vram_budget_gb": args.vram_budget_gb, "prefetch_k": args.prefetch_k,
                    "pinned_module_mirror": not args.no_mirror, "prefetch_wraparound": not args.no_wraparound,
                    "l2": "weights larger than L2; no flush"},

@@ -339,6 +339,11 @@ int32_t sh_vmm_create_slab(uint64_t allocator, uint64_t total_bytes, int32_t* sl
 int32_t sh_vmm_define_region(uint64_t allocator, int32_t slab, uint64_t offset, uint64_t size, int32_t* region_out);
 int32_t sh_vmm_ensure_resident(uint64_t allocator, int32_t slab, int32_t region, int32_t hold, void** dev_ptr_out);
 int32_t sh_vmm_release(uint64_t allocator, int32_t slab, int32_t region, uint64_t stream);
+/* Background prefetch (reference: vmm_src/prefetch.rs, python.rs:82-85): the request is queued and one worker
+ * thread maps the region; best effort, a request that finds no room is dropped.  sh_vmm_prefetch_wait returns
+ * when the queue is empty and the worker idle (SH_ERR_TIMEOUT after timeout_ms). */
+int32_t sh_vmm_prefetch_async(uint64_t allocator, int32_t slab, int32_t region);
+int32_t sh_vmm_prefetch_wait(uint64_t allocator, int32_t timeout_ms);
 int32_t sh_vmm_set_priority(uint64_t allocator, int32_t slab, uint32_t priority);
 int32_t sh_vmm_set_ceiling(uint64_t allocator, uint64_t ceiling_bytes);
 int32_t sh_vmm_destroy_slab(uint64_t allocator, int32_t slab);

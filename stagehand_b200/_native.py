@@ -121,6 +121,8 @@ _SIGNATURES: dict[str, list] = {
     "sh_vmm_define_region": [c_uint64, c_int32, c_uint64, c_uint64, POINTER(c_int32)],
     "sh_vmm_ensure_resident": [c_uint64, c_int32, c_int32, c_int32, POINTER(c_void_p)],
     "sh_vmm_release": [c_uint64, c_int32, c_int32, c_uint64],
+    "sh_vmm_prefetch_async": [c_uint64, c_int32, c_int32],
+    "sh_vmm_prefetch_wait": [c_uint64, c_int32],
     "sh_vmm_set_priority": [c_uint64, c_int32, c_uint32],
     "sh_vmm_set_ceiling": [c_uint64, c_uint64],
     "sh_vmm_destroy_slab": [c_uint64, c_int32],

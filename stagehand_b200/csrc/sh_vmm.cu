@@ -5,7 +5,9 @@
 // eviction.rs, handle.rs): same verbs and the same policy -- a region is evictable when nobody holds
 // it (refcount 0) and its release event has completed; victims go lowest slab priority first, least
 // recently used first (vmm_src/eviction.rs:15-144).  Differences: one mutex instead of the lock-free
-// fast path, a synchronous prefetch instead of a worker thread, and every wait is bounded.
+// fast path, and every wait is bounded.  sh_vmm_prefetch_async hands the mapping to one worker thread, as
+// the reference's prefetch does (vmm_src/prefetch.rs); sh_vmm_ensure_resident with hold = 0 still maps in
+// the calling thread.
 //
 // The driver entry points are resolved at run time (cudaGetDriverEntryPoint), so the library still
 // loads on a host that has no GPU driver.
@@ -18,7 +20,9 @@
 #include <chrono>
 #include <cstdarg>
 #include <cstdio>
+#include <condition_variable>
 #include <cstring>
+#include <deque>
 #include <map>
 #include <mutex>
 #include <thread>
@@ -102,6 +106,12 @@ struct Allocator {
     std::map<int, Slab> slabs;
     std::mutex mu;
     CUmemAllocationProp prop{};
+    // background prefetch: (slab, region) requests served by one worker thread under `mu`
+    std::deque<std::pair<int, int>> requests;
+    std::condition_variable wake, idle;
+    std::thread worker;
+    bool worker_started = false, worker_busy = false, stopping = false;
+    int64_t prefetch_failures = 0;
 };
 
 size_t round_up(size_t v, size_t g) { return (v + g - 1) / g * g; }
@@ -248,6 +258,15 @@ int32_t sh_vmm_create(int32_t device, uint64_t ceiling_bytes, uint64_t* allocato
 int32_t sh_vmm_destroy(uint64_t allocator) {
     Allocator* a = as_alloc(allocator);
     if (a == nullptr) return SH_OK;
+    if (a->worker_started) {
+        {
+            std::lock_guard<std::mutex> lk(a->mu);
+            a->stopping = true;
+            a->requests.clear();
+        }
+        a->wake.notify_all();
+        a->worker.join();
+    }
     {
         std::lock_guard<std::mutex> lk(a->mu);
         for (auto& [sid, s] : a->slabs) {
@@ -298,6 +317,55 @@ int32_t sh_vmm_define_region(uint64_t allocator, int32_t slab, uint64_t offset, 
     s->regions.push_back(r);
     *region_out = static_cast<int32_t>(s->regions.size() - 1);
     return SH_OK;
+}
+
+static void prefetch_loop(Allocator* a) {
+    (void)cudaSetDevice(a->device);
+    (void)cudaFree(nullptr);                       // the primary context becomes current on this thread
+    std::unique_lock<std::mutex> lk(a->mu);
+    for (;;) {
+        a->wake.wait(lk, [a] { return a->stopping || !a->requests.empty(); });
+        if (a->stopping) break;
+        const std::pair<int, int> req = a->requests.front();
+        a->requests.pop_front();
+        a->worker_busy = true;
+        Slab* s = nullptr;
+        Region* r = nullptr;
+        // best effort: a request for something destroyed meanwhile, or one that finds no room, is dropped
+        if (find(*a, req.first, req.second, &s, &r) == SH_OK && !r->mapped) {
+            if (map_region(*a, req.first, *s, req.second, *r) != SH_OK) a->prefetch_failures += 1;
+            else r->last_access = ++a->clock;
+        }
+        a->worker_busy = false;
+        if (a->requests.empty()) a->idle.notify_all();
+    }
+}
+
+int32_t sh_vmm_prefetch_async(uint64_t allocator, int32_t slab, int32_t region) {
+    Allocator* a = as_alloc(allocator);
+    if (a == nullptr) return vfail(SH_ERR_INVALID_ARG, "null allocator");
+    std::lock_guard<std::mutex> lk(a->mu);
+    Slab* s = nullptr;
+    Region* r = nullptr;
+    const int rc = find(*a, slab, region, &s, &r);
+    if (rc != SH_OK) return rc;
+    if (r->mapped) return SH_OK;
+    if (!a->worker_started) {
+        a->worker = std::thread(prefetch_loop, a);
+        a->worker_started = true;
+    }
+    a->requests.emplace_back(slab, region);
+    a->wake.notify_one();
+    return SH_OK;
+}
+
+int32_t sh_vmm_prefetch_wait(uint64_t allocator, int32_t timeout_ms) {
+    Allocator* a = as_alloc(allocator);
+    if (a == nullptr) return vfail(SH_ERR_INVALID_ARG, "null allocator");
+    std::unique_lock<std::mutex> lk(a->mu);
+    const bool done = a->idle.wait_for(lk, std::chrono::milliseconds(timeout_ms < 0 ? 0 : timeout_ms),
+                                       [a] { return a->requests.empty() && !a->worker_busy; });
+    return done ? SH_OK : vfail(SH_ERR_TIMEOUT, "prefetch requests still pending after %d ms", timeout_ms);
 }
 
 int32_t sh_vmm_ensure_resident(uint64_t allocator, int32_t slab, int32_t region, int32_t hold, void** dev_ptr_out) {

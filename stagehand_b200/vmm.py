@@ -115,8 +115,12 @@ class SlabAllocator:
                               int(stream))
 
     def prefetch(self, slab: int, region: int) -> None:
-        """Map the region ahead of use without holding it."""
-        _raise(self._lib.sh_vmm_ensure_resident(self._handle, int(slab), int(region), 0, None), "prefetch")
+        """Ask the background worker to map the region ahead of use (not held; best effort)."""
+        _raise(self._lib.sh_vmm_prefetch_async(self._handle, int(slab), int(region)), "prefetch")
+
+    def wait_prefetch(self, timeout_ms: int = 10_000) -> None:
+        """Block until every queued prefetch has been served."""
+        _raise(self._lib.sh_vmm_prefetch_wait(self._handle, int(timeout_ms)), "wait_prefetch")
 
     def set_priority(self, slab: int, priority: int) -> None:
         _raise(self._lib.sh_vmm_set_priority(self._handle, int(slab), int(priority)), "set_priority")

@@ -77,6 +77,7 @@ def test_priority_decides_the_victim_and_prefetch_maps_without_holding(alloc: Sl
     alloc.set_priority(keep, 10)
     alloc.prefetch(keep, rk)                                  # mapped first (oldest), but high priority
     alloc.prefetch(spare, rs)
+    alloc.wait_prefetch()                                     # the worker thread serves requests in order
     assert alloc.stats()["mapped_regions"] == 2
     h = alloc.ensure_resident(third, rt)                      # the low-priority slab is evicted although it is newer
     hk = alloc.ensure_resident(keep, rk)                      # still mapped: no new eviction
@@ -103,3 +104,29 @@ def test_matmul_on_mapped_tensors(alloc: SlabAllocator) -> None:
         ha.as_tensor("float32", [8 << 20])
     ha.release()
     hb.release()
+
+
+def test_background_prefetch_overlaps_the_caller(alloc: SlabAllocator) -> None:
+    """prefetch() returns at once; the worker maps in the background; a later ensure_resident is a hit."""
+    import time
+
+    g = alloc.stats()["granularity"]
+    size = 64 * g
+    slab = alloc.create_slab(8 * size)
+    regions = [alloc.define_region(slab, i * size, size) for i in range(8)]
+    t0 = time.perf_counter()
+    for r in regions:
+        alloc.prefetch(slab, r)
+    queued_s = time.perf_counter() - t0
+    alloc.wait_prefetch()
+    assert alloc.stats()["mapped_regions"] == 8
+    t0 = time.perf_counter()
+    handles = [alloc.ensure_resident(slab, r) for r in regions]
+    hit_s = time.perf_counter() - t0
+    assert queued_s < 0.05 and hit_s < 0.05                  # neither maps anything in the calling thread
+    for h in handles:
+        h.release()
+    alloc.prefetch(slab, regions[0])                          # already mapped: nothing queued
+    alloc.wait_prefetch(1000)
+    with pytest.raises(ValueError):
+        alloc.prefetch(slab, 999)

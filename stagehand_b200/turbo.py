@@ -146,9 +146,13 @@ class TurboConductor:
     WINDOW = 3
 
     def __init__(self, model: nn.Module, block_pattern: str = r".*\.block\.\d+$", dtype: torch.dtype = torch.bfloat16,
-                 device: int = 0, vram_budget_gb: float = 18.0) -> None:
+                 device: int = 0, vram_budget_gb: float = 18.0, squareq_path: str | None = None) -> None:
         if not is_available():
             raise RuntimeError("the native transfer engine needs a CUDA device and the built library")
+        self._model, self._block_pattern = model, block_pattern
+        self._squareq_path = squareq_path          # a SquareQ slab (.fpk / .sqpk): blocks rotate as packed INT8 images
+        self._layouts: list[list[tuple]] = []      # INT8 mode: (name, shape, dtype, offset, numel) per block
+        self._parked: list[dict[str, torch.Tensor]] = []
         self._dtype, self._device_idx = dtype, int(device)
         self._device = torch.device("cuda", self._device_idx)
         matcher = re.compile(block_pattern)
@@ -167,8 +171,61 @@ class TurboConductor:
     def num_blocks(self) -> int:
         return len(self._block_modules)
 
+    def _prepare_squareq(self) -> None:
+        """INT8 mode: every block is registered as its packed SquareQ image and expanded into its slot.
+
+        The registry conversion and the image planning are the streaming runtime's own
+        (``convert_registry_to_file_backed`` + the packed-image planner); a short-lived runtime is
+        built for them and shut down once every image is staged in the engine's page-locked memory.
+        """
+        from stagehand_b200.config import StagehandConfig
+        from stagehand_b200.runtime import StagehandRuntime
+
+        cfg = StagehandConfig(pinned_pool_mb=2048, pinned_slab_mb=1024, telemetry_enabled=False, nan_inf_check=False,
+                              strict_bf16=False, packed_image_cache_mb=0)
+        rt = StagehandRuntime(self._model, cfg, block_pattern=self._block_pattern, dtype=self._dtype, inference_mode=True)
+        try:
+            rt.convert_registry_to_file_backed(str(self._squareq_path))
+            by_id = {e.block_id: e for e in rt._registry.blocks_in_order()}
+            entries = [by_id[name] for name in self._block_names]
+            if any(not e.squareq_backed for e in entries):
+                raise ValueError("every matched block must be SquareQ-backed by the given slab")
+            engine = TransferEngine()
+            plans = []
+            for entry in entries:
+                plan = rt._scheduler._image_plan(entry)
+                engine.register_int8_block(plan.descs, plan.n_descs, plan.total_bytes, entry.size_bytes, plan.out_dtype_code)
+                plans.append(plan)
+                self._layouts.append(list(entry.param_layout))
+            engine.initialize(self._device_idx, self.WINDOW)
+            scratch = torch.empty(max(p.total_bytes for p in plans), dtype=torch.uint8)
+            for index, (entry, plan) in enumerate(zip(entries, plans)):
+                scratch[: plan.total_bytes].zero_()
+                plan.fill_static(scratch, threads=8)
+                plan.refresh_dynamic(scratch, entry.module_ref(), {})
+                engine.stage_block(index, [scratch.data_ptr()])
+                # what the parameters point at while the block is not in a slot: module-owned ones keep their
+                # CPU values, SquareQ-sourced ones are empty (their source is the image), as in the runtime
+                parked = {}
+                for name, _shape, dtype, _off, _numel in entry.param_layout:
+                    live = _param(entry.module_ref(), name).data
+                    parked[name] = live if live.numel() else torch.empty(0, dtype=dtype)
+                self._parked.append(parked)
+            capacity = max(e.size_bytes for e in entries)
+            for slot in range(engine.num_gpu_slots()):
+                tensor = torch.empty(capacity, dtype=torch.uint8, device=self._device)
+                engine.set_slot_gpu_ptrs(slot, [tensor.data_ptr()])
+                self._slot_tensors.append([tensor])
+        finally:
+            rt.shutdown()
+        self._engine, self._prepared = engine, True
+        log.info("TurboConductor: ready, %d slots, %d INT8 blocks", engine.num_gpu_slots(), len(entries))
+
     def prepare(self) -> None:
         if self._prepared:
+            return
+        if self._squareq_path is not None:
+            self._prepare_squareq()
             return
         engine = TransferEngine()
         for mod in self._block_modules:
@@ -203,11 +260,22 @@ class TurboConductor:
         slot = self._engine.block_slot(block_idx)
         if slot is None:
             raise RuntimeError(f"Block {block_idx} has no GPU slot after step()")
+        if self._layouts:
+            flat = self._slot_tensors[slot][0]
+            module = self._block_modules[block_idx]
+            for name, shape, dtype, off, numel in self._layouts[block_idx]:
+                _param(module, name).data = flat[off : off + numel * dtype.itemsize].view(dtype).reshape(shape)
+            return
         for param_idx, (_n, p) in enumerate(self._block_modules[block_idx].named_parameters()):
             shape = self._param_meta[block_idx][param_idx][1]
             p.data = self._slot_tensors[slot][param_idx][: p_numel(shape)].reshape(shape)
 
     def after_block(self, block_idx: int) -> None:
+        if self._layouts:
+            module = self._block_modules[block_idx]
+            for name, tensor in self._parked[block_idx].items():
+                _param(module, name).data = tensor
+            return
         for param_idx, (_n, p) in enumerate(self._block_modules[block_idx].named_parameters()):
             p.data = self._cpu_tensors[block_idx][param_idx]
 
@@ -223,6 +291,14 @@ class TurboConductor:
     def shutdown(self) -> None:
         if self._engine is not None:
             self._engine.drain()
+        if self._layouts:
+            for index in range(len(self._block_modules)):
+                self.after_block(index)
+            self._slot_tensors.clear()
+            if self._engine is not None:
+                self._engine.close()
+                self._engine = None
+            return
         self._slot_tensors.clear()     # parameters already point at host views; drop the GPU window
         for index in range(len(self._block_modules)):
             for param_idx, (_n, p) in enumerate(self._block_modules[index].named_parameters()):
@@ -231,6 +307,14 @@ class TurboConductor:
         if self._engine is not None:
             self._engine.close()
             self._engine = None
+
+
+def _param(module: nn.Module, dotted: str) -> nn.Parameter:
+    *path, leaf = dotted.split(".")
+    node = module
+    for part in path:
+        node = getattr(node, part)
+    return node._parameters[leaf]
 
 
 def p_numel(shape: tuple[int, ...]) -> int:

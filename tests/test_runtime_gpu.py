@@ -437,3 +437,44 @@ def test_adapter_training_over_a_squareq_base(tmp_path: Path) -> None:
         assert last.evictions >= 4 and last.dequant_launches >= 8         # forward and backward both reload
     assert rt._scheduler._streamer.read_status() == 0
     rt.shutdown()
+
+
+def test_turbo_conductor_rotates_squareq_blocks(tmp_path: Path) -> None:
+    """``TurboConductor(..., squareq_path=...)``: the slot-rotation wrapper over packed INT8 images.
+
+    Same golden forward as the streaming runtime, block images bit-identical to the reference's host dequant.
+    """
+    from stagehand_b200.turbo import TurboConductor
+
+    kw, tokens = CFGS["cfg1"]
+    torch.manual_seed(0)
+    model = TinyBlockModel(**kw)
+    for p in model.parameters():
+        p.requires_grad_(False)
+    fpk = tmp_path / "cfg1.fpk"
+    write_squareq_fpk(model, BLOCK_PATTERNS["tiny"], fpk, seed=0)
+    x = torch.randn(1, tokens, kw["hidden"], generator=torch.Generator().manual_seed(0)).to(torch.bfloat16).cuda()
+    conductor = TurboConductor(model, block_pattern=BLOCK_PATTERNS["tiny"], dtype=torch.bfloat16,
+                               device=torch.cuda.current_device(), squareq_path=str(fpk))
+    conductor.prepare()
+    engine = conductor._engine
+    assert (engine.num_blocks(), engine.num_gpu_slots()) == (4, 3)
+    want = [str(d) for d in G["cfg1__block_sha256"]]
+    for _sweep in range(2):
+        h = x
+        with torch.inference_mode():
+            for i, block in enumerate(model.blocks):
+                conductor.before_block(i, "forward")
+                if _sweep == 0:
+                    torch.cuda.current_stream().synchronize()
+                    slot = engine.block_slot(i)
+                    size = int(G["cfg1__block_bytes"][i])
+                    image = conductor._slot_tensors[slot][0][:size].cpu().numpy()
+                    assert hashlib.sha256(image.tobytes()).hexdigest() == want[i]
+                h = block(h)
+                conductor.after_block(i)
+                assert block.qkv.weight.numel() == 0 and block.norm1.weight.device.type == "cpu"
+        torch.cuda.synchronize()
+        assert _rel_l2(h, "cfg1") <= 1e-2
+    conductor.evict_all()
+    conductor.shutdown()

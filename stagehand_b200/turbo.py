@@ -194,6 +194,10 @@ class TurboConductor:
             plans = []
             for entry in entries:
                 plan = rt._scheduler._image_plan(entry)
+                if plan.dynamic_rows:
+                    # staging the module-owned rows settles their descriptor kinds, which the engine copies now
+                    settle = torch.empty(plan.total_bytes - plan.static_bytes, dtype=torch.uint8)
+                    plan.refresh_dynamic(settle, entry.module_ref(), {}, base_offset=plan.static_bytes)
                 engine.register_int8_block(plan.descs, plan.n_descs, plan.total_bytes, entry.size_bytes, plan.out_dtype_code)
                 plans.append(plan)
                 self._layouts.append(list(entry.param_layout))

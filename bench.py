@@ -70,6 +70,8 @@ def parse_args() -> argparse.Namespace:
                     help="stop the prefetch window at the last block, as the reference does (each step then starts cold)")
     ap.add_argument("--int8", action="store_true",
                     help="rotation: blocks are packed INT8 images expanded into their slot (no write-back)")
+    ap.add_argument("--squareq", action="store_true",
+                    help="video_train: the frozen weights are a SquareQ INT8 slab (adapter training over an INT8 base)")
     ap.add_argument("--module-backed", action="store_true",
                     help="video_train: no checkpoint files; the frozen weights live on the module as CPU parameters")
     ap.add_argument("--training-lookahead", action="store_true",
@@ -486,7 +488,12 @@ def run_video_training(args) -> None:
         model.init_adapters(seed=0, std=0.02)
         for name, p in model.named_parameters():
             p.requires_grad_("lora" in name)
-        if args.module_backed:
+        if args.squareq:
+            from stagehand_b200.workloads import write_squareq_fpk
+
+            sq = write_squareq_fpk(model, BLOCK_PATTERNS["video"], tmp / "base.fpk", seed=0, share_storage=True)
+            info = {"bytes": sq["elements"]}
+        elif args.module_backed:
             # the frozen weights as ordinary CPU parameters (one random draw per shape, copied into every layer)
             from torch import nn
 
@@ -512,7 +519,10 @@ def run_video_training(args) -> None:
             backward_prefetch=not args.no_backward_prefetch, training_lookahead=args.training_lookahead)
         rt = sh.StagehandRuntime(model, cfg, block_pattern=BLOCK_PATTERNS["video"], group="dit", dtype=torch.bfloat16,
                                  inference_mode=False)
-        converted = 0 if args.module_backed else rt.convert_registry_to_file_backed_sharded(str(tmp / "ckpt"))
+        if args.squareq:
+            converted = rt.convert_registry_to_file_backed(str(tmp / "base.fpk"))
+        else:
+            converted = 0 if args.module_backed else rt.convert_registry_to_file_backed_sharded(str(tmp / "ckpt"))
         g = torch.Generator().manual_seed(0)
         x_host = torch.randn(1, args.tokens, hidden, generator=g).to(torch.bfloat16).pin_memory()
         c_host = torch.randn(1, 512, hidden, generator=g).to(torch.bfloat16).pin_memory()
@@ -575,9 +585,9 @@ def run_video_training(args) -> None:
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"video-DiT-shaped {built} blocks (of {n_blocks} asked), hidden {hidden}, {heads} heads, "
                                    f"FFN {ffn}, self + cross attention, bf16 weights "
-                                   f"{'held by the module (no file)' if args.module_backed else 'from sharded safetensors'}, "
+                                   f"{'as a SquareQ INT8 slab' if args.squareq else 'held by the module (no file)' if args.module_backed else 'from sharded safetensors'}, "
                                    f"{args.tokens}+512 tokens, forward + backward, rank-{rank_r} adapters, checkpointed blocks",
-                       "frozen_weights": info["bytes"] // 2, "converted_params": converted,
+                       "frozen_weights": info["bytes"] if args.squareq else info["bytes"] // 2, "converted_params": converted,
                        "vram_budget_gb": budget_gb, "prefetch_k": args.prefetch_k,
                        "backward_prefetch": not args.no_backward_prefetch,
                        "training_lookahead": args.training_lookahead,

@@ -450,11 +450,15 @@ BLOCK_PATTERNS = {
 
 def synth_squareq_layer(out_features: int, in_features: int, generator: torch.Generator,
                         padded_in: int | None = None, has_bias: bool = True,
-                        zero_point_nonzero: bool = False) -> dict[str, torch.Tensor]:
-    """One layer dict ``{qweight, scale, zero_point, bias}`` with the synthetic value distributions."""
+                        zero_point_nonzero: bool = False, scale_median: float = 0.01) -> dict[str, torch.Tensor]:
+    """One layer dict ``{qweight, scale, zero_point, bias}`` with the synthetic value distributions.
+
+    *scale_median* is the median of the lognormal row scales (0.01 in the named configurations; a model whose
+    projections have no compensating gain uses a smaller one so that activations stay finite in bf16).
+    """
     padded = int(padded_in) if padded_in is not None else in_features
     q = torch.randint(-127, 128, (out_features, padded), dtype=torch.int8, generator=generator)
-    scale = torch.exp(torch.randn(out_features, generator=generator) * 0.5 + math.log(0.01)).float()
+    scale = torch.exp(torch.randn(out_features, generator=generator) * 0.5 + math.log(scale_median)).float()
     if zero_point_nonzero:
         zp = torch.randint(-8, 9, (out_features,), generator=generator).float() * 0.5
     else:
@@ -466,7 +470,8 @@ def synth_squareq_layer(out_features: int, in_features: int, generator: torch.Ge
 
 
 def write_squareq_fpk(model: nn.Module, block_pattern: str, path: str | Path, seed: int = 0,
-                      share_storage: bool = False, pad_in_to: int | None = None) -> dict[str, int]:
+                      share_storage: bool = False, pad_in_to: int | None = None,
+                      scale_median: float = 0.01) -> dict[str, int]:
     """Write a SquareQ BP8 ``.fpk`` covering every ``nn.Linear`` inside the matched blocks.
 
     Layer names are ``"<block_id>.<linear path>"``.  With *share_storage* every
@@ -497,7 +502,8 @@ def write_squareq_fpk(model: nn.Module, block_pattern: str, path: str | Path, se
             if share_storage and key in by_shape:
                 layer = by_shape[key]
             else:
-                layer = synth_squareq_layer(out_f, in_f, generator, padded_in=padded, has_bias=has_bias)
+                layer = synth_squareq_layer(out_f, in_f, generator, padded_in=padded, has_bias=has_bias,
+                                            scale_median=scale_median)
                 by_shape[key] = layer
             name = f"{block_id}.{sub_name}" if sub_name else block_id
             layers[name] = dict(layer)

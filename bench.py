@@ -18,6 +18,11 @@ bf16 weight bytes per second (whole job, all GPUs) and milliseconds per streamed
 * ``roofline`` -- the block kernel against HBM: 3 bytes per weight / its mean launch duration.
 * ``cpu_baseline`` -- the reference's host dequant (same ATen ops, all host threads) on a bounded sample.
 
+Other workloads (``--workload``), each printing one JSON line of its own: ``kernel_sweep`` (per-matrix
+block-kernel sweep), ``flux_mistral`` (Mistral-shaped encoder + the DiT, for 2/4/8 GPUs), ``video_train``
+(forward + backward with rank-32 adapters over bf16 safetensors, module-held bf16 or SquareQ INT8 frozen
+weights), ``flux_bf16`` (module-backed bf16 inference), ``rotation`` and ``vmm`` (the engines beside the path).
+
 Weights are synthetic (seeded; the shapes and value distributions of the named configuration).
 Inputs are far larger than L2 (11.8 GB of INT8 stream through per step), so no L2 flush is needed.
 """

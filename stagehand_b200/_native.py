@@ -9,7 +9,7 @@ import ctypes
 from ctypes import POINTER, byref, c_char_p, c_double, c_float, c_int32, c_int64, c_size_t, c_uint8, c_uint32, c_uint64, c_void_p
 from pathlib import Path
 
-from stagehand_b200.errors import StagehandOOMError, TransferError
+from stagehand_b200.errors import TransferError, raise_for_status
 
 __all__ = [
     "ShParamDesc", "ShDeviceInfo", "ShStats", "lib", "is_built", "check", "LIB_PATH", "EXPORTED_SYMBOLS",
@@ -175,12 +175,7 @@ def check(status: int, what: str = "") -> int:
     if status == SH_OK or status == SH_ERR_BUSY:
         return status
     text = last_error()
-    msg = f"{what}: {text}" if what else text
-    if status == SH_ERR_OOM:
-        raise StagehandOOMError(msg)
-    if status == SH_ERR_INVALID_ARG:
-        raise ValueError(msg)
-    raise TransferError(f"{msg} (status {status})")
+    return raise_for_status(status, f"{what}: {text}" if what else text)
 
 
 def make_descs(rows: list[ShParamDesc]):

@@ -325,3 +325,41 @@ def test_training_schedules_on_a_counted_budget(mode: str) -> None:
 
 
 test_training_schedules_on_a_counted_budget.results = {}
+
+
+def test_status_codes_map_to_the_reference_exception_types() -> None:
+    from stagehand_b200.errors import raise_for_status
+
+    assert raise_for_status(_native.SH_OK, "x") == 0 and raise_for_status(_native.SH_ERR_BUSY, "x") == _native.SH_ERR_BUSY
+    with pytest.raises(sh.StagehandOOMError):
+        raise_for_status(_native.SH_ERR_OOM, "no room")
+    with pytest.raises(ValueError):
+        raise_for_status(_native.SH_ERR_INVALID_ARG, "bad")
+    for code in (_native.SH_ERR_CUDA, _native.SH_ERR_TIMEOUT, _native.SH_ERR_UNSUPPORTED):
+        with pytest.raises(sh.TransferError, match=f"status {code}"):
+            raise_for_status(code, "native")
+    assert issubclass(sh.TransferError, sh.StagehandError) and issubclass(sh.DtypeMismatchError, sh.StagehandError)
+    assert sh.InvalidStateTransitionError.__name__ == "InvalidStateTransitionError"
+
+
+def test_sharded_safetensors_writer_is_read_back_by_the_safetensors_library(tmp_path: Path) -> None:
+    from safetensors import safe_open
+
+    from stagehand_b200.workloads import VideoShapedDiT, write_sharded_safetensors
+
+    model = VideoShapedDiT(n_blocks=3, hidden=32, heads=2, ffn=64, rank=2, dtype=torch.bfloat16)
+    for name, p in model.named_parameters():
+        p.requires_grad_("lora" in name)
+    info = write_sharded_safetensors(model, tmp_path, blocks_per_shard=2, seed=1, share_values=True)
+    assert info == {"tensors": 30, "bytes": 3 * (8 * 32 * 32 + 2 * 32 * 64) * 2, "shards": 2}
+    index = __import__("json").loads((tmp_path / "model.safetensors.index.json").read_text())["weight_map"]
+    assert len(index) == 30 and set(index.values()) == {"model-00001-of-00002.safetensors", "model-00002-of-00002.safetensors"}
+    seen = {}
+    for shard in sorted(tmp_path.glob("*.safetensors")):
+        with safe_open(str(shard), framework="pt") as fh:
+            for key in fh.keys():
+                seen[key] = fh.get_tensor(key)
+    assert set(seen) == set(index)
+    a, b = seen["blocks.0.attn_q.base.weight"], seen["blocks.2.cross_o.base.weight"]
+    assert a.dtype == torch.bfloat16 and tuple(a.shape) == (32, 32) and torch.equal(a, b)      # one draw per shape
+    assert tuple(seen["blocks.1.fc1.weight"].shape) == (64, 32)

@@ -156,6 +156,14 @@ class LayerRuntime:
 
     # ── hooks ────────────────────────────────────────────────────────
 
+    def _post_hook(self, layer_id: str):
+        """Post-forward hook; registered to run always, so a forward abandoned by an exception drops its reference."""
+        def hook(_module, _args, output) -> None:
+            if output is None and self._residency.get_entry(layer_id).refcount == 0:
+                return      # the forward failed before the layer was taken: nothing to drop
+            self._scheduler.after_block(layer_id, _first_tensor(output))
+        return hook
+
     def _install_hooks(self, order: list[str], traced: bool) -> None:
         for layer_id in order:
             module = self._layer_map.get(layer_id)
@@ -163,9 +171,7 @@ class LayerRuntime:
                 continue
             pre = self._scheduled_pre_hook(layer_id) if traced else self._trace_pre_hook(layer_id)
             self._hook_handles.append(module.register_forward_pre_hook(pre))
-            self._hook_handles.append(module.register_forward_hook(
-                lambda _m, _a, out, lid=layer_id: self._scheduler.after_block(lid, _first_tensor(out)),
-                always_call=True))         # a forward abandoned by an exception still drops its reference
+            self._hook_handles.append(module.register_forward_hook(self._post_hook(layer_id), always_call=True))
         if not self._inference_mode:
             for layer_id in (reversed(order) if traced else order):
                 module = self._layer_map.get(layer_id)

@@ -327,6 +327,10 @@ def cpu_dequant_sample(min_seconds: float, max_reps: int, pinned: bool, warmup: 
     from oracle.torch_port import host_stage_weights
     from stagehand_b200.workloads import synth_squareq_layer
 
+    # all host cores, also under a launcher that exports OMP_NUM_THREADS=1 for its ranks (only one rank runs this)
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    if torch.get_num_threads() < cores:
+        torch.set_num_threads(cores)
     g = torch.Generator().manual_seed(0)
     shapes = [(9216, 3072), (21504, 3072), (3072, 15360)]
     weights = [synth_squareq_layer(o, i, g, has_bias=False) for o, i in shapes]

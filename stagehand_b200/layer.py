@@ -273,6 +273,11 @@ class LayerRuntime:
         return self._mode == "scheduled"
 
     @property
+    def num_layers(self) -> int:
+        """Managed layers discovered at wrap time, traced or not (reference ``layer.py:593-595``)."""
+        return len(self._all_layer_names)
+
+    @property
     def trace_order(self) -> list[str]:
         return list(self._trace_order)
 

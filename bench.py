@@ -157,7 +157,7 @@ def build_workload(args, tmp: Path, device: str):
     """Model on the meta device + its synthetic SquareQ slab file + pinned host inputs."""
     import torch
 
-    from stagehand_b200.workloads import (BLOCK_PATTERNS, FluxShapedDiT, materialize_small_params,
+    from synthetic_workloads import (BLOCK_PATTERNS, FluxShapedDiT, materialize_small_params,
                                           write_squareq_fpk)
 
     if args.workload == "flux_small":          # a reduced model for quick functional runs only
@@ -168,7 +168,7 @@ def build_workload(args, tmp: Path, device: str):
     with torch.device("meta"):
         model = FluxShapedDiT(dtype=torch.bfloat16, **kw)
         if with_encoder:        # the sharded multi-GPU configuration: a Mistral-24B-shaped text encoder in front
-            from stagehand_b200.workloads import EncoderPlusDiT, MistralShapedEncoder
+            from synthetic_workloads import EncoderPlusDiT, MistralShapedEncoder
 
             model = EncoderPlusDiT(MistralShapedEncoder(dtype=torch.bfloat16), model)
     materialize_small_params(model)
@@ -325,7 +325,7 @@ def cpu_dequant_sample(min_seconds: float, max_reps: int, pinned: bool, warmup: 
     import torch
 
     from oracle.torch_port import host_stage_weights
-    from stagehand_b200.workloads import synth_squareq_layer
+    from synthetic_workloads import synth_squareq_layer
 
     # all host cores, also under a launcher that exports OMP_NUM_THREADS=1 for its ranks (only one rank runs this)
     cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
@@ -472,7 +472,7 @@ def run_video_training(args) -> None:
 
     import stagehand_b200 as sh
     from stagehand_b200 import _native as native
-    from stagehand_b200.workloads import BLOCK_PATTERNS, VideoShapedDiT, materialize_small_params, write_sharded_safetensors
+    from synthetic_workloads import BLOCK_PATTERNS, VideoShapedDiT, materialize_small_params, write_sharded_safetensors
 
     torch.cuda.set_device(0)
     peaks = measured_peaks()
@@ -498,7 +498,7 @@ def run_video_training(args) -> None:
         for name, p in model.named_parameters():
             p.requires_grad_("lora" in name)
         if args.squareq:
-            from stagehand_b200.workloads import write_squareq_fpk
+            from synthetic_workloads import write_squareq_fpk
 
             # row scales with median 0.00024: weights of standard deviation ~0.02, like the bf16 variants of this workload
             sq = write_squareq_fpk(model, BLOCK_PATTERNS["video"], tmp / "base.fpk", seed=0, share_storage=True,
@@ -625,7 +625,7 @@ def run_module_bf16(args) -> None:
 
     import stagehand_b200 as sh
     from stagehand_b200 import _native as native
-    from stagehand_b200.workloads import BLOCK_PATTERNS, FluxShapedDiT, _SYNTH_WEIGHT_STD
+    from synthetic_workloads import BLOCK_PATTERNS, FluxShapedDiT, _SYNTH_WEIGHT_STD
 
     torch.cuda.set_device(0)
     K, W = args.steps, max(args.warmup, 0)

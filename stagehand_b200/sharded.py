@@ -32,7 +32,7 @@ from stagehand_b200._native import (SH_DESC_ABSOLUTE, SH_DESC_PEER_SOURCE, SH_KI
 from stagehand_b200.errors import TransferError
 
 __all__ = ["ShardPlan", "plan_shards", "StripePiece", "StripeDesc", "BlockStripes", "plan_block_stripes",
-           "DeviceImageStore", "park_images_in_hbm", "shard_images_over_ranks"]
+           "DeviceImageStore", "close_arenas_in_order", "park_images_in_hbm", "shard_images_over_ranks"]
 
 _ALIGN = 4096
 
@@ -160,6 +160,22 @@ def plan_block_stripes(static_descs: Sequence[Any], itemsize: int, world: int, h
 # ── the store ────────────────────────────────────────────────────────────
 
 
+def close_arenas_in_order(drain, barrier, unmap_peers, free_own) -> None:
+    """The order in which a rank lets go of the shared arenas.
+
+    1. *drain*: this rank's GPU has finished everything it queued (its kernels and copies read peers' arenas);
+    2. *barrier*: so has every other rank -- from here on nobody reads anybody's arena;
+    3. *unmap_peers*: drop this rank's mappings of the other arenas;
+    4. *barrier*: every mapping of this rank's arena is gone;
+    5. *free_own*: only now is the arena itself released.
+    """
+    drain()
+    barrier()
+    unmap_peers()
+    barrier()
+    free_own()
+
+
 class DeviceImageStore:
     """This rank's arena of INT8 static images (or stripes) plus mappings of the peers' arenas.
 
@@ -178,6 +194,8 @@ class DeviceImageStore:
         if layout not in ("owner", "striped"):
             raise ValueError(f"unknown shard layout {layout!r}")
         self._lib = _native.lib()
+        self._group = group
+        self._closed = False
         self._emulated = emulate_world > 1
         if self._emulated:
             rank, world = 0, emulate_world
@@ -311,14 +329,41 @@ class DeviceImageStore:
         return sum(self.arena_bytes[r] for r in (range(self.world) if self._emulated else [self.rank]))
 
     def close(self) -> None:
-        """Unmap the peers' arenas and free this process's.  Call after the runtime has shut down."""
-        for ptr in self._opened:
-            self._lib.sh_ipc_close(ptr)
-        self._opened.clear()
-        for ptr in self._owned:
-            self._lib.sh_device_free(ptr)
-        self._owned.clear()
-        self._arenas.clear()
+        """Unmap the peers' arenas and free this process's.
+
+        Collective when the store spans several processes: every rank of the group must call it, after its
+        own runtime has shut down.  Other ranks' block kernels and copy engines read this rank's arena in
+        place, so nothing is unmapped or freed before every rank has drained its own GPU and met the others
+        at a barrier, and no arena is freed before every rank has dropped its mappings of it
+        (:func:`close_arenas_in_order`).  A rank that cannot reach the barrier must not call this; its arena
+        then stays allocated until the process exits.
+        """
+        if self._closed:
+            return
+        self._closed = True
+        collective = self.world > 1 and not self._emulated
+
+        def drain() -> None:
+            torch.cuda.synchronize()
+
+        def barrier() -> None:
+            if collective:
+                import torch.distributed as dist
+
+                dist.barrier(group=self._group)
+
+        def unmap() -> None:
+            for ptr in self._opened:
+                self._lib.sh_ipc_close(ptr)
+            self._opened.clear()
+
+        def free() -> None:
+            for ptr in self._owned:
+                self._lib.sh_device_free(ptr)
+            self._owned.clear()
+            self._arenas.clear()
+
+        close_arenas_in_order(drain, barrier, unmap, free)
 
 
 def park_images_in_hbm(runtime: Any, fused: bool = True) -> DeviceImageStore:

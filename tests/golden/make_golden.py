@@ -204,7 +204,7 @@ def stage_block_case(ref_stage) -> dict[str, np.ndarray]:
 def runtime_forward(tmp: Path) -> dict[str, np.ndarray]:
     """Reference runtime, CPU block mode, on the named small configuration and a smaller one."""
     import stagehand
-    from stagehand_b200.workloads import BLOCK_PATTERNS, TinyBlockModel, write_squareq_fpk
+    from synthetic_workloads import BLOCK_PATTERNS, TinyBlockModel, write_squareq_fpk
 
     out: dict[str, np.ndarray] = {}
     for tag, kw, tokens in (

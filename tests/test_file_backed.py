@@ -149,7 +149,7 @@ def _video_pair(tmp_path: Path, dtype: torch.dtype = torch.float32):
     """A small adapter-carrying DiT streamed from a sharded checkpoint, and a resident twin with the same values."""
     from safetensors import safe_open
 
-    from stagehand_b200.workloads import VideoShapedDiT, write_sharded_safetensors
+    from synthetic_workloads import VideoShapedDiT, write_sharded_safetensors
 
     kw = dict(n_blocks=4, hidden=64, heads=4, ffn=128, rank=4, dtype=dtype)
     model = VideoShapedDiT(**kw)
@@ -256,7 +256,7 @@ def test_gpu_backward_pass_prefetches_downwards(tmp_path: Path) -> None:
     """With ``backward_prefetch`` block i-1 is already in flight when block i's gradient arrives."""
     import gc
 
-    from stagehand_b200.workloads import VideoShapedDiT, write_sharded_safetensors
+    from synthetic_workloads import VideoShapedDiT, write_sharded_safetensors
 
     demand: dict[object, int] = {}
     grads: dict[object, list[torch.Tensor]] = {}

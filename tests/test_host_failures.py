@@ -19,7 +19,7 @@ from desc_interp import expand
 import stagehand_b200 as sh
 from stagehand_b200 import _native
 from stagehand_b200.packed import plan_block_image
-from stagehand_b200.workloads import BLOCK_PATTERNS, TinyBlockModel, synth_squareq_layer, write_squareq_fpk
+from synthetic_workloads import BLOCK_PATTERNS, TinyBlockModel, synth_squareq_layer, write_squareq_fpk
 
 
 def _runtime(model: nn.Module, **kw) -> sh.StagehandRuntime:

@@ -16,7 +16,7 @@ from desc_interp import expand
 import stagehand_b200 as sh
 from stagehand_b200 import _native
 from stagehand_b200.packed import plan_block_image
-from stagehand_b200.workloads import BLOCK_PATTERNS, TinyBlockModel, write_squareq_fpk
+from synthetic_workloads import BLOCK_PATTERNS, TinyBlockModel, write_squareq_fpk
 
 
 def test_library_exports_every_declared_symbol() -> None:
@@ -345,7 +345,7 @@ def test_status_codes_map_to_the_reference_exception_types() -> None:
 def test_sharded_safetensors_writer_is_read_back_by_the_safetensors_library(tmp_path: Path) -> None:
     from safetensors import safe_open
 
-    from stagehand_b200.workloads import VideoShapedDiT, write_sharded_safetensors
+    from synthetic_workloads import VideoShapedDiT, write_sharded_safetensors
 
     model = VideoShapedDiT(n_blocks=3, hidden=32, heads=2, ffn=64, rank=2, dtype=torch.bfloat16)
     for name, p in model.named_parameters():

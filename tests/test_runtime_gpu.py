@@ -14,7 +14,7 @@ import torch
 
 from conftest import GOLDEN
 import stagehand_b200 as sh
-from stagehand_b200.workloads import BLOCK_PATTERNS, TinyBlockModel, write_squareq_fpk
+from synthetic_workloads import BLOCK_PATTERNS, TinyBlockModel, write_squareq_fpk
 
 pytestmark = pytest.mark.gpu
 
@@ -382,7 +382,7 @@ def test_adapter_training_over_a_squareq_base(tmp_path: Path) -> None:
     """
     import copy
 
-    from stagehand_b200.workloads import VideoShapedDiT
+    from synthetic_workloads import VideoShapedDiT
 
     kw = dict(n_blocks=4, hidden=64, heads=4, ffn=128, rank=4, dtype=torch.float32)
     model = VideoShapedDiT(**kw)

@@ -149,3 +149,40 @@ def test_stripes_cover_every_row_once_and_rebuild_the_block() -> None:
         if world == 8:                                          # the load is spread: no rank holds most of the bytes
             per_rank = [sum(p.nbytes for p in stripes.pieces if p.rank == r) for r in range(world)]
             assert max(per_rank) < 0.4 * sum(per_rank)
+
+
+def _close_rank_main(rank: int, world: int, port: int, out_dir: str) -> None:
+    """Every rank logs its close steps with a timestamp; rank 1 is late to its own close."""
+    import time
+
+    from stagehand_b200.sharded import close_arenas_in_order
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        log: list[tuple[str, float]] = []
+        if rank == 1:
+            time.sleep(0.5)                                   # still "computing" on the peers' arenas
+        close_arenas_in_order(lambda: log.append(("drain", time.monotonic())), dist.barrier,
+                              lambda: log.append(("unmap", time.monotonic())),
+                              lambda: log.append(("free", time.monotonic())))
+        gathered: list = [None] * world
+        dist.all_gather_object(gathered, log)
+        if rank == 0:
+            last_drain = max(t for entries in gathered for name, t in entries if name == "drain")
+            last_unmap = max(t for entries in gathered for name, t in entries if name == "unmap")
+            first_unmap = min(t for entries in gathered for name, t in entries if name == "unmap")
+            first_free = min(t for entries in gathered for name, t in entries if name == "free")
+            assert all([name for name, _ in entries] == ["drain", "unmap", "free"] for entries in gathered)
+            assert last_drain <= first_unmap          # nobody unmaps while any rank may still be reading
+            assert last_unmap <= first_free           # nobody frees an arena another rank still maps
+            open(os.path.join(out_dir, "ordered"), "w").write("ok")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_close_waits_for_every_rank_before_unmapping_or_freeing(tmp_path) -> None:
+    # CLOCK_MONOTONIC is shared by the processes of one host, so the ranks' timestamps compare directly
+    world = 2
+    mp.spawn(_close_rank_main, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert (tmp_path / "ordered").exists()

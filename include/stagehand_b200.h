@@ -96,7 +96,7 @@ typedef struct ShStats {
     int64_t h2d_bytes;
     int64_t peer_copies;          /* device-to-device copies issued (local or peer source)    */
     int64_t peer_bytes;
-    int64_t kernel_status_errors; /* launches whose device status word came back non-zero     */
+    int64_t kernel_status_errors; /* status-word read-backs (sh_status_poll) that came back non-zero */
 } ShStats;
 
 /* ── library ─────────────────────────────────────────────────────────── */
@@ -236,6 +236,124 @@ int32_t sh_stream_block_async(const ShParamDesc* descs, int32_t n_descs,
                               uint64_t ev_copied, uint64_t ev_ready, int32_t* status_dev);
 
 /*
+ * Non-blocking watch on a device status word (the `status_dev` handed to the block-kernel calls).  Each call
+ * looks at the previous read-back if it has landed -- a non-zero word is ORed into the sticky bits returned
+ * in *bits_out and counted in ShStats.kernel_status_errors -- and queues the next one on `stream`: a
+ * device-to-host copy of the word followed by clearing it, so bits set by later launches on that stream are
+ * seen by a later poll.  Bits: 1 = a scale fetch timed out and plain loads were used (results correct),
+ * 2 = a descriptor with an unknown path was skipped (its destination bytes are stale).  Meant to be called
+ * once per step; sh_status_forget drops the watch (before the word's memory is freed).  The reference has
+ * no device code and therefore no counterpart.
+ */
+int32_t sh_status_poll(int32_t* status_dev, uint64_t stream, int32_t* bits_out);
+int32_t sh_status_forget(int32_t* status_dev);
+
+/* ── registered blocks: validate and plan once, load with one call ───── */
+
+/* where sh_block_load takes the packed image from */
+#define SH_SRC_HOST    0   /* src = page-locked host image: one copy over the host link into staging_dev  */
+#define SH_SRC_DEVICE  1   /* src = the image in device memory (this GPU's, or a peer's with               */
+                           /* SH_DESC_PEER_SOURCE descriptors): the kernel reads it in place, no staging    */
+#define SH_SRC_GATHER  2   /* the pieces given to sh_block_set_gather are pulled into staging_dev by copy   */
+                           /* engines (one cudaMemcpyAsync each); src is unused                             */
+
+/* `bytes` at device address `src_dev` (this GPU's memory or a peer's mapped arena) land at staging_dev + staging_off */
+typedef struct ShGatherPiece {
+    uint64_t src_dev;
+    uint64_t staging_off;
+    uint64_t bytes;
+} ShGatherPiece;
+
+/*
+ * Arguments of one load.  Streams and events are raw handles; an event field of 0 means "none".
+ *   ev_staging_free  the copy stream(s) wait for it before overwriting staging_dev (the kernel that last read it)
+ *   ev_out_free      the dequant stream waits for it before writing out_dev (the slab's previous readers)
+ *   ev_src_ready     the dequant stream waits for it before the kernel (e.g. a side copy the absolute
+ *                    descriptors read from)
+ *   ev_copied/2      recorded on copy_stream once every copy of this load has been queued behind it
+ *   ev_ready/2/3     recorded on dequant_stream after the block kernel (one for the consumer, one for the
+ *                    staging slab's next writer, one for whatever else the kernel read)
+ * copy_stream2 (0 = none) takes every second piece of a gather so that two copy engines run side by side.
+ * staging_dev and out_dev (and src for SH_SRC_DEVICE) must be 256-byte aligned.
+ */
+typedef struct ShBlockLoad {
+    const void* src;
+    void*       staging_dev;
+    void*       out_dev;
+    int32_t*    status_dev;
+    uint64_t    copy_stream;
+    uint64_t    copy_stream2;
+    uint64_t    dequant_stream;
+    uint64_t    ev_staging_free;
+    uint64_t    ev_out_free;
+    uint64_t    ev_src_ready;
+    uint64_t    ev_copied;
+    uint64_t    ev_copied2;
+    uint64_t    ev_ready;
+    uint64_t    ev_ready2;
+    uint64_t    ev_ready3;
+    int32_t     src_kind;
+    int32_t     reserved;
+} ShBlockLoad;
+
+/*
+ * sh_block_register checks a block's descriptors (as sh_dequant_block_async does) against an image of
+ * packed_bytes and a slab of out_bytes and builds its launch plans once; the handle is then loaded any number
+ * of times with sh_block_load, which does no validation beyond its pointers and never blocks:
+ *   copy stream(s):  wait ev_staging_free; host copy or gather copies into staging_dev; record ev_copied
+ *   dequant stream:  wait for the copies, ev_out_free and ev_src_ready; block kernel; record ev_ready
+ * Descriptors flagged SH_DESC_ABSOLUTE keep their addresses; the others are offsets into whatever image the
+ * load names (staging_dev, or src for SH_SRC_DEVICE).  A failed call may have queued its copies already; it
+ * never launches a kernel on bad arguments.
+ *
+ * Replaces, per block load, _stage_block_to_host + submit_h2d (src/stagehand/scheduler.py:953-987,
+ * src/stagehand/transfer.py:108-143); registration replaces TransferEngine::register_block
+ * (turbo_src/engine.rs:82-100) for packed INT8 blocks.
+ */
+int32_t sh_block_register(const ShParamDesc* descs, int32_t n_descs, size_t packed_bytes, size_t out_bytes,
+                          int32_t out_dtype, uint64_t* block_out);
+int32_t sh_block_set_gather(uint64_t block, const ShGatherPiece* pieces, int32_t n_pieces);
+int32_t sh_block_load(uint64_t block, const ShBlockLoad* args);
+int32_t sh_block_unregister(uint64_t block);
+
+/* ── VRAM slab pool ──────────────────────────────────────────────────── */
+
+typedef struct ShPoolStats {
+    int64_t slabs;
+    int64_t held_slabs;
+    int64_t total_bytes;
+    int64_t free_bytes;
+    int64_t acquires;
+    int64_t reuses;       /* acquires that found a slab released earlier (and ordered the writer after its readers) */
+} ShPoolStats;
+
+/*
+ * Output slabs of the streaming path.  The memory is the caller's (torch allocations, so that the
+ * watermarks of the budget manager see it -- as the reference's engine takes slot pointers from torch,
+ * turbo_src/engine.rs:361-372); the pool keeps which slab is free, which block holds which slot and the
+ * event that guards a slab's reuse.
+ *   sh_vram_pool_create     n_slabs may be 0; slabs can be added later     engine.rs:140-152 (slot table)
+ *   sh_vram_pool_add_slab   a new slab, free                              set_slot_gpu_ptrs, engine.rs:361-372
+ *   sh_slab_acquire         smallest free slab of `bytes` .. `max_bytes` (max_bytes = bytes: exact size; 0: no
+ *                           upper limit) for block_id; writer_stream is ordered (on the device) after the
+ *                           slab's release event; SH_ERR_BUSY when none is free
+ *   sh_slab_release         records the release event on reader_stream and frees the slot
+ *   sh_vram_pool_remove_slab  forgets a free slab so its memory can go: waits (bounded) for its release event,
+ *                           or not at all with timeout_ms < 0 when the memory's next user is ordered behind
+ *                           the releasing stream anyway (a stream-ordered allocator)
+ *   sh_block_location       slot held by block_id, or -1                  block_slot, engine.rs:375-394
+ */
+int32_t sh_vram_pool_create(int32_t n_slabs, const uint64_t* base_ptrs, const uint64_t* slab_bytes, uint64_t* pool_out);
+int32_t sh_vram_pool_add_slab(uint64_t pool, uint64_t base_ptr, uint64_t bytes, int32_t* slot_out);
+int32_t sh_slab_acquire(uint64_t pool, const char* block_id, uint64_t bytes, uint64_t max_bytes, uint64_t writer_stream,
+                        int32_t* slot_out, uint64_t* ptr_out);
+int32_t sh_slab_release(uint64_t pool, int32_t slot, uint64_t reader_stream);
+int32_t sh_vram_pool_remove_slab(uint64_t pool, int32_t slot, int32_t timeout_ms);
+int32_t sh_block_location(uint64_t pool, const char* block_id, int32_t* slot_out);
+int32_t sh_vram_pool_stats(uint64_t pool, ShPoolStats* out);
+int32_t sh_vram_pool_destroy(uint64_t pool);
+
+/*
  * Cap, in CTAs per SM, on block-kernel launches that read another GPU's memory
  * (descriptors flagged SH_DESC_PEER_SOURCE); 0 lifts it (the default).  Such a
  * launch runs at the pace of its NVLink reads; capped, it leaves most of every
@@ -255,6 +373,24 @@ int32_t sh_set_peer_ctas_per_sm(int32_t ctas_per_sm);
 int32_t sh_profile_enable(int32_t on);
 int32_t sh_profile_collect(double* kernel_ms_out, int64_t* launches_out, int64_t* elements_out,
                            int64_t* bytes_out, int32_t timeout_ms);
+
+/*
+ * The same records without waiting: sh_profile_poll sums the ones whose GPU work has finished -- block-kernel
+ * time per block, and (for sh_block_load) the time its copies took on the copy stream -- and leaves the rest
+ * for a later poll.  This is what fills copy_time_ms / dequant_time_ms of the runtime's per-step telemetry
+ * (the reference declares copy_time_ms and never fills it, src/stagehand/telemetry.py:31).
+ */
+typedef struct ShProfileSums {
+    double  kernel_ms;
+    double  copy_ms;
+    int64_t kernel_blocks;     /* blocks whose kernel time is in kernel_ms        */
+    int64_t copies;            /* block loads whose copy time is in copy_ms       */
+    int64_t elements;          /* int8 weights expanded by those kernels          */
+    int64_t kernel_bytes;      /* their algorithmic HBM bytes                     */
+    int64_t copy_bytes;        /* bytes moved by those copies                     */
+    int64_t pending;           /* records still running, left for the next poll   */
+} ShProfileSums;
+int32_t sh_profile_poll(ShProfileSums* out);
 
 /* ── slot-rotation transfer engine ───────────────────────────────────── */
 
@@ -356,13 +492,17 @@ int32_t sh_vmm_last_error(char* buf, int32_t buf_len);
  * not grow its footprint, a loop where an allocation would stall the device).  It is
  * sh_stream_block_async on ONE stream with the staging slab replaced by a fixed array inside the
  * library's device image: SH_NOALLOC_MAX_BYTES per GPU that loads the library, held until exit.
- * It calls no cudaMalloc / cudaFree and no allocating library routine; the caller passes the host
- * image and the output slab as usual.
+ * Once set up it calls no cudaMalloc / cudaFree and no allocating library routine; the caller passes
+ * the host image and the output slab as usual.
  *
  *   - packed_bytes above SH_NOALLOC_MAX_BYTES (or more than 128 descriptors) fails with
  *     SH_ERR_INVALID_ARG and a message; nothing is enqueued.
- *   - The first call on a device resolves the array's device address (cudaGetSymbolAddress) with
- *     that device current; make that first call before any stream capture begins.
+ *   - The array's device address is resolved (cudaGetSymbolAddress) once per device, with that device
+ *     current: by sh_init(device), or else by the first call of this entry point on the device.  That
+ *     is also the moment CUDA loads this part of the library onto the GPU and the array's memory is
+ *     taken -- so call sh_init (or make one warm-up call) on every device BEFORE handing the device's
+ *     memory to another allocator, and before any stream capture begins.  A process that skips both
+ *     can see this entry point's first call fail for lack of memory.
  *   - Every call shares the one array, which keeps the previous call's bytes.  Nothing in it has to
  *     start at zero -- each call overwrites every byte its kernel reads -- but two calls whose GPU
  *     work overlaps (different streams, no ordering between them) race on it: serialise them.

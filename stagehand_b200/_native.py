@@ -12,7 +12,8 @@ from pathlib import Path
 from stagehand_b200.errors import TransferError, raise_for_status
 
 __all__ = [
-    "ShParamDesc", "ShDeviceInfo", "ShStats", "lib", "is_built", "check", "LIB_PATH", "EXPORTED_SYMBOLS",
+    "ShParamDesc", "ShDeviceInfo", "ShStats", "ShGatherPiece", "ShBlockLoad", "ShPoolStats",
+    "SH_SRC_HOST", "SH_SRC_DEVICE", "SH_SRC_GATHER", "lib", "is_built", "check", "LIB_PATH", "EXPORTED_SYMBOLS",
     "SH_KIND_DEQUANT_I8", "SH_KIND_CAST_F32", "SH_KIND_COPY", "SH_KIND_ZERO",
     "SH_DT_BF16", "SH_DT_F16", "SH_DT_F32", "SH_DESC_PEER_SOURCE", "SH_DESC_ABSOLUTE",
     "SH_OK", "SH_ERR_INVALID_ARG", "SH_ERR_OOM", "SH_ERR_CUDA", "SH_ERR_TIMEOUT", "SH_ERR_BUSY", "SH_ERR_UNSUPPORTED",
@@ -59,6 +60,36 @@ class ShStats(ctypes.Structure):
         ("kernel_status_errors", c_int64),
     ]
 
+
+class ShGatherPiece(ctypes.Structure):
+    _fields_ = [("src_dev", c_uint64), ("staging_off", c_uint64), ("bytes", c_uint64)]
+
+
+class ShBlockLoad(ctypes.Structure):
+    _fields_ = [
+        ("src", c_void_p), ("staging_dev", c_void_p), ("out_dev", c_void_p), ("status_dev", c_void_p),
+        ("copy_stream", c_uint64), ("copy_stream2", c_uint64), ("dequant_stream", c_uint64),
+        ("ev_staging_free", c_uint64), ("ev_out_free", c_uint64), ("ev_src_ready", c_uint64),
+        ("ev_copied", c_uint64), ("ev_copied2", c_uint64), ("ev_ready", c_uint64), ("ev_ready2", c_uint64), ("ev_ready3", c_uint64),
+        ("src_kind", c_int32), ("reserved", c_int32),
+    ]
+
+
+class ShPoolStats(ctypes.Structure):
+    _fields_ = [
+        ("slabs", c_int64), ("held_slabs", c_int64), ("total_bytes", c_int64), ("free_bytes", c_int64),
+        ("acquires", c_int64), ("reuses", c_int64),
+    ]
+
+
+class ShProfileSums(ctypes.Structure):
+    _fields_ = [
+        ("kernel_ms", c_double), ("copy_ms", c_double), ("kernel_blocks", c_int64), ("copies", c_int64),
+        ("elements", c_int64), ("kernel_bytes", c_int64), ("copy_bytes", c_int64), ("pending", c_int64),
+    ]
+
+
+SH_SRC_HOST, SH_SRC_DEVICE, SH_SRC_GATHER = 0, 1, 2
 
 _P_DESC = POINTER(ShParamDesc)
 
@@ -128,9 +159,24 @@ _SIGNATURES: dict[str, list] = {
     "sh_vmm_destroy_slab": [c_uint64, c_int32],
     "sh_vmm_stats": [c_uint64, POINTER(ShVmmStats)],
     "sh_vmm_last_error": [c_char_p, c_int32],
+    "sh_status_poll": [c_void_p, c_uint64, POINTER(c_int32)],
+    "sh_status_forget": [c_void_p],
+    "sh_block_register": [_P_DESC, c_int32, c_size_t, c_size_t, c_int32, POINTER(c_uint64)],
+    "sh_block_set_gather": [c_uint64, POINTER(ShGatherPiece), c_int32],
+    "sh_block_load": [c_uint64, POINTER(ShBlockLoad)],
+    "sh_block_unregister": [c_uint64],
+    "sh_vram_pool_create": [c_int32, POINTER(c_uint64), POINTER(c_uint64), POINTER(c_uint64)],
+    "sh_vram_pool_add_slab": [c_uint64, c_uint64, c_uint64, POINTER(c_int32)],
+    "sh_slab_acquire": [c_uint64, c_char_p, c_uint64, c_uint64, c_uint64, POINTER(c_int32), POINTER(c_uint64)],
+    "sh_slab_release": [c_uint64, c_int32, c_uint64],
+    "sh_vram_pool_remove_slab": [c_uint64, c_int32, c_int32],
+    "sh_block_location": [c_uint64, c_char_p, POINTER(c_int32)],
+    "sh_vram_pool_stats": [c_uint64, POINTER(ShPoolStats)],
+    "sh_vram_pool_destroy": [c_uint64],
     "sh_set_peer_ctas_per_sm": [c_int32],
     "sh_profile_enable": [c_int32],
     "sh_profile_collect": [POINTER(c_double), POINTER(c_int64), POINTER(c_int64), POINTER(c_int64), c_int32],
+    "sh_profile_poll": [POINTER(ShProfileSums)],
 }
 EXPORTED_SYMBOLS = tuple(_SIGNATURES)
 

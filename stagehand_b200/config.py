@@ -76,6 +76,13 @@ class StagehandConfig:
     # only parameters that require gradients (and the gradients) are copied back, asynchronously.  Hosts without
     # CUDA always take the copy path.
     pinned_module_mirror: bool = True
+    # Per-block device timings in the step metrics (copy_time_ms, dequant_time_ms, exposed_stall_ms): CUDA timing
+    # events around every block's copies and kernel and around the compute stream's wait for the block; they are
+    # polled at step end, never waited for.  Process-wide (it switches the library's launch profiling on).
+    telemetry_block_timings: bool = False
+    # NVTX ranges on the host thread around each block's submission ("stagehand.load <block> [host|device|gather]")
+    # and around the point where the compute stream is made to wait for it ("stagehand.wait <block>").
+    nvtx_ranges: bool = False
     # Where the block slabs in VRAM come from: "torch" (caching allocator) or "vmm" (the C++ virtual-memory
     # slab allocator: parked slabs can be unmapped under `vmm_ceiling_mb` without fragmenting anything).
     device_pool_backend: str = "torch"

@@ -1,8 +1,7 @@
 // C ABI of the SquareQ streaming path (declarations and reference citations:
 // include/stagehand_b200.h).  Thin, non-blocking wrappers over the CUDA runtime
 // plus the launcher of the block kernel.  No torch types, no interpreter calls.
-#include "../../include/stagehand_b200.h"
-#include "sq_block_kernel.cuh"
+#include "sh_common.h"
 
 #include <algorithm>
 #include <atomic>
@@ -10,11 +9,12 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <map>
 #include <mutex>
 #include <thread>
 #include <vector>
 
-namespace {
+namespace shc {
 
 thread_local char g_err[512] = "";
 
@@ -31,30 +31,20 @@ int cuda_fail(cudaError_t e, const char* what) {
     return fail(code, "%s: %s (%d)", what, cudaGetErrorString(e), static_cast<int>(e));
 }
 
-#define SH_CUDA(call, what)                                   \
-    do {                                                      \
-        cudaError_t e__ = (call);                             \
-        if (e__ != cudaSuccess) return cuda_fail(e__, what);  \
-    } while (0)
-
-inline cudaStream_t as_stream(uint64_t s) { return reinterpret_cast<cudaStream_t>(static_cast<uintptr_t>(s)); }
-inline cudaEvent_t as_event(uint64_t e) { return reinterpret_cast<cudaEvent_t>(static_cast<uintptr_t>(e)); }
-
-struct Counters {
-    std::atomic<int64_t> launches{0}, elements{0}, h2d_copies{0}, h2d_bytes{0}, peer_copies{0}, peer_bytes{0},
-        status_errors{0};
-} g_ctr;
+Counters g_ctr;
 
 // per-launch timing records
 struct ProfRecord {
     cudaEvent_t start, stop;
     int64_t elements, bytes;
+    int kind;                       // 0 = block-kernel launch(es) of one block, 1 = the copies of one block load
 };
 std::mutex g_prof_mu;
 std::vector<ProfRecord> g_prof_pending;
 std::vector<cudaEvent_t> g_prof_free;
 std::atomic<int> g_prof_on{0};
 
+// call with g_prof_mu held
 cudaEvent_t prof_event() {
     if (!g_prof_free.empty()) {
         cudaEvent_t e = g_prof_free.back();
@@ -66,7 +56,6 @@ cudaEvent_t prof_event() {
     return e;
 }
 
-// Polls an event until done or until the deadline; never blocks without bound.
 int wait_event_bounded(cudaEvent_t ev, int timeout_ms) {
     const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms < 0 ? 0 : timeout_ms);
     int spins = 0;
@@ -78,6 +67,70 @@ int wait_event_bounded(cudaEvent_t ev, int timeout_ms) {
         if (++spins > 200) std::this_thread::sleep_for(std::chrono::microseconds(50));
     }
 }
+
+int launch_plans(const sq::BlockPlan* plans, int n_plans, int64_t elements, int64_t traffic, int out_dtype,
+                 cudaStream_t stream, int32_t* status_dev) {
+    ProfRecord rec{nullptr, nullptr, elements, traffic, 0};
+    const bool prof = g_prof_on.load(std::memory_order_relaxed) != 0;
+    if (prof) {
+        std::lock_guard<std::mutex> lk(g_prof_mu);
+        rec.start = prof_event();
+        rec.stop = prof_event();
+        if (rec.start == nullptr || rec.stop == nullptr) {       // only one could be had: give it back, time nothing
+            if (rec.start != nullptr) g_prof_free.push_back(rec.start);
+            if (rec.stop != nullptr) g_prof_free.push_back(rec.stop);
+            rec.start = rec.stop = nullptr;
+        }
+    }
+    if (rec.start) cudaEventRecord(rec.start, stream);
+    for (int p = 0; p < n_plans; ++p) {
+        const cudaError_t e = sq::launch_plan(plans[p], out_dtype, stream, status_dev);
+        if (e != cudaSuccess) {
+            if (rec.start) {
+                std::lock_guard<std::mutex> lk(g_prof_mu);
+                g_prof_free.push_back(rec.start);
+                g_prof_free.push_back(rec.stop);
+            }
+            return cuda_fail(e, "block kernel launch");
+        }
+        g_ctr.launches.fetch_add(1, std::memory_order_relaxed);
+    }
+    if (rec.stop) {
+        cudaEventRecord(rec.stop, stream);
+        std::lock_guard<std::mutex> lk(g_prof_mu);
+        g_prof_pending.push_back(rec);
+    }
+    g_ctr.elements.fetch_add(elements, std::memory_order_relaxed);
+    return SH_OK;
+}
+
+bool copy_timing_begin(cudaStream_t stream, cudaEvent_t* start_out, cudaEvent_t* stop_out) {
+    if (g_prof_on.load(std::memory_order_relaxed) == 0) return false;
+    {
+        std::lock_guard<std::mutex> lk(g_prof_mu);
+        *start_out = prof_event();
+        *stop_out = prof_event();
+        if (*start_out == nullptr || *stop_out == nullptr) {
+            if (*start_out != nullptr) g_prof_free.push_back(*start_out);
+            if (*stop_out != nullptr) g_prof_free.push_back(*stop_out);
+            return false;
+        }
+    }
+    cudaEventRecord(*start_out, stream);
+    return true;
+}
+
+void copy_timing_end(cudaStream_t stream, cudaEvent_t start, cudaEvent_t stop, int64_t bytes) {
+    cudaEventRecord(stop, stream);
+    std::lock_guard<std::mutex> lk(g_prof_mu);
+    g_prof_pending.push_back(ProfRecord{start, stop, 0, bytes, 1});
+}
+
+}  // namespace shc
+
+namespace {
+
+using namespace shc;
 
 int launch_block(const ShParamDesc* descs, int32_t n, const void* packed, size_t packed_bytes, void* out,
                  size_t out_bytes, int32_t out_dtype, cudaStream_t stream, int32_t* status_dev) {
@@ -92,30 +145,22 @@ int launch_block(const ShParamDesc* descs, int32_t n, const void* packed, size_t
     const int rc = sq::build_plans(descs, n, packed, packed_bytes, out, out_bytes, out_dtype, plans.data(), &n_plans,
                                    &elements, &traffic, err, sizeof(err));
     if (rc != SH_OK) return fail(rc, "%s", err);
-
-    ProfRecord rec{nullptr, nullptr, elements, traffic};
-    const bool prof = g_prof_on.load(std::memory_order_relaxed) != 0;
-    if (prof) {
-        std::lock_guard<std::mutex> lk(g_prof_mu);
-        rec.start = prof_event();
-        rec.stop = prof_event();
-    }
-    if (rec.start) cudaEventRecord(rec.start, stream);
-    for (int p = 0; p < n_plans; ++p) {
-        const cudaError_t e = sq::launch_plan(plans[p], out_dtype, stream, status_dev);
-        if (e != cudaSuccess) return cuda_fail(e, "block kernel launch");
-        g_ctr.launches.fetch_add(1, std::memory_order_relaxed);
-    }
-    if (rec.stop) cudaEventRecord(rec.stop, stream);
-    if (prof && rec.start && rec.stop) {
-        std::lock_guard<std::mutex> lk(g_prof_mu);
-        g_prof_pending.push_back(rec);
-    }
-    g_ctr.elements.fetch_add(elements, std::memory_order_relaxed);
-    return SH_OK;
+    return launch_plans(plans.data(), n_plans, elements, traffic, out_dtype, stream, status_dev);
 }
 
+// Read-back state of one device status word (sh_status_poll).
+struct StatusWatch {
+    int32_t* host = nullptr;        // page-locked landing word
+    cudaEvent_t landed = nullptr;
+    bool pending = false;
+    int32_t sticky = 0;             // every bit ever seen
+};
+std::mutex g_status_mu;
+std::map<int32_t*, StatusWatch> g_status;
+
 }  // namespace
+
+using namespace shc;
 
 extern "C" {
 
@@ -141,6 +186,13 @@ int32_t sh_init(int32_t device) {
     if (prop.major != 10)
         return fail(SH_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library carries sm_100a code only", device, prop.major,
                     prop.minor);
+    // Load the library's device image on this GPU now -- with it the fixed staging array of
+    // sh_dequant_from_host_noalloc -- so that its memory is paid for here, not at that entry point's first call.
+    // Best effort: if the array cannot be had (no memory left), only that entry point is affected and it
+    // reports the failure itself when called.
+    char why[200];
+    (void)noalloc_prepare_current_device(why, sizeof(why));
+    (void)cudaGetLastError();
     return SH_OK;
 }
 
@@ -153,6 +205,12 @@ int32_t sh_shutdown(void) {
     g_prof_pending.clear();
     for (auto e : g_prof_free) cudaEventDestroy(e);
     g_prof_free.clear();
+    std::lock_guard<std::mutex> lk2(g_status_mu);
+    for (auto& [dev, w] : g_status) {
+        if (w.landed != nullptr) cudaEventDestroy(w.landed);
+        if (w.host != nullptr) cudaFreeHost(w.host);
+    }
+    g_status.clear();
     return SH_OK;
 }
 
@@ -403,28 +461,72 @@ int32_t sh_stream_block_async(const ShParamDesc* descs, int32_t n_descs, const v
     if (packed_host == nullptr || staging_dev == nullptr) return fail(SH_ERR_INVALID_ARG, "null image pointer");
     if (copy_stream != dequant_stream && ev_copied == 0)
         return fail(SH_ERR_INVALID_ARG, "two streams need ev_copied to order the kernel after the copy");
-    // validate before anything is enqueued so a bad descriptor leaves both streams untouched
-    {
-        const int max_plans = (std::max(n_descs, 1) + sq::kMaxDescs - 1) / sq::kMaxDescs;
-        std::vector<sq::BlockPlan> plans(static_cast<size_t>(max_plans));
-        int n_plans = 0;
-        char err[256];
-        if (n_descs < 0 || (n_descs > 0 && descs == nullptr)) return fail(SH_ERR_INVALID_ARG, "null descriptor array");
-        const int rc = sq::build_plans(descs, n_descs, staging_dev, packed_bytes, out_dev, out_bytes, out_dtype,
-                                       plans.data(), &n_plans, nullptr, nullptr, err, sizeof(err));
-        if (rc != SH_OK) return fail(rc, "%s", err);
-    }
-    int rc = sh_copy_h2d_async(staging_dev, packed_host, packed_bytes, copy_stream);
+    // validate before anything is enqueued so a bad descriptor leaves both streams untouched; the plans
+    // built for the check are the ones launched
+    if (n_descs < 0 || (n_descs > 0 && descs == nullptr)) return fail(SH_ERR_INVALID_ARG, "null descriptor array");
+    if (n_descs > 0 && out_dev == nullptr) return fail(SH_ERR_INVALID_ARG, "null output slab");
+    const int max_plans = (std::max(n_descs, 1) + sq::kMaxDescs - 1) / sq::kMaxDescs;
+    std::vector<sq::BlockPlan> plans(static_cast<size_t>(max_plans));
+    int n_plans = 0;
+    int64_t elements = 0, traffic = 0;
+    char err[256];
+    int rc = sq::build_plans(descs, n_descs, staging_dev, packed_bytes, out_dev, out_bytes, out_dtype, plans.data(),
+                             &n_plans, &elements, &traffic, err, sizeof(err));
+    if (rc != SH_OK) return fail(rc, "%s", err);
+    rc = sh_copy_h2d_async(staging_dev, packed_host, packed_bytes, copy_stream);
     if (rc != SH_OK) return rc;
     if (ev_copied != 0) {
         SH_CUDA(cudaEventRecord(as_event(ev_copied), as_stream(copy_stream)), "cudaEventRecord");
         if (copy_stream != dequant_stream)
             SH_CUDA(cudaStreamWaitEvent(as_stream(dequant_stream), as_event(ev_copied), 0), "cudaStreamWaitEvent");
     }
-    rc = launch_block(descs, n_descs, staging_dev, packed_bytes, out_dev, out_bytes, out_dtype,
-                      as_stream(dequant_stream), status_dev);
+    rc = launch_plans(plans.data(), n_plans, elements, traffic, out_dtype, as_stream(dequant_stream), status_dev);
     if (rc != SH_OK) return rc;
     if (ev_ready != 0) SH_CUDA(cudaEventRecord(as_event(ev_ready), as_stream(dequant_stream)), "cudaEventRecord");
+    return SH_OK;
+}
+
+int32_t sh_status_poll(int32_t* status_dev, uint64_t stream, int32_t* bits_out) {
+    if (status_dev == nullptr) return fail(SH_ERR_INVALID_ARG, "null status word");
+    std::lock_guard<std::mutex> lk(g_status_mu);
+    StatusWatch& w = g_status[status_dev];
+    if (w.host == nullptr) {
+        SH_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&w.host), sizeof(int32_t), cudaHostAllocPortable), "cudaHostAlloc");
+        *w.host = 0;
+        SH_CUDA(cudaEventCreateWithFlags(&w.landed, cudaEventDisableTiming), "cudaEventCreate");
+    }
+    if (w.pending) {
+        const cudaError_t q = cudaEventQuery(w.landed);
+        if (q == cudaErrorNotReady) {                       // the previous read-back has not landed: nothing new to say
+            if (bits_out != nullptr) *bits_out = w.sticky;
+            return SH_OK;
+        }
+        if (q != cudaSuccess) return cuda_fail(q, "cudaEventQuery");
+        w.pending = false;
+        if (*w.host != 0) {
+            w.sticky |= *w.host;
+            g_ctr.status_errors.fetch_add(1, std::memory_order_relaxed);
+        }
+    }
+    // next read-back, ordered on `stream` behind the launches queued so far; the word is cleared behind it,
+    // so bits set by later launches on that stream are seen by the next poll and none is lost
+    SH_CUDA(cudaMemcpyAsync(w.host, status_dev, sizeof(int32_t), cudaMemcpyDeviceToHost, as_stream(stream)),
+            "cudaMemcpyAsync D2H");
+    SH_CUDA(cudaMemsetAsync(status_dev, 0, sizeof(int32_t), as_stream(stream)), "cudaMemsetAsync");
+    SH_CUDA(cudaEventRecord(w.landed, as_stream(stream)), "cudaEventRecord");
+    w.pending = true;
+    if (bits_out != nullptr) *bits_out = w.sticky;
+    return SH_OK;
+}
+
+int32_t sh_status_forget(int32_t* status_dev) {
+    std::lock_guard<std::mutex> lk(g_status_mu);
+    auto it = g_status.find(status_dev);
+    if (it == g_status.end()) return SH_OK;
+    if (it->second.pending) (void)wait_event_bounded(it->second.landed, 10000);
+    if (it->second.landed != nullptr) cudaEventDestroy(it->second.landed);
+    if (it->second.host != nullptr) cudaFreeHost(it->second.host);
+    g_status.erase(it);
     return SH_OK;
 }
 
@@ -450,7 +552,7 @@ int32_t sh_profile_collect(double* kernel_ms_out, int64_t* launches_out, int64_t
     int rc = SH_OK;
     for (auto& r : recs) {
         if (rc == SH_OK) rc = wait_event_bounded(r.stop, timeout_ms);
-        if (rc == SH_OK) {
+        if (rc == SH_OK && r.kind == 0) {
             float t = 0.f;
             if (cudaEventElapsedTime(&t, r.start, r.stop) == cudaSuccess) {
                 ms += t;
@@ -472,6 +574,41 @@ int32_t sh_profile_collect(double* kernel_ms_out, int64_t* launches_out, int64_t
     if (elements_out) *elements_out = elements;
     if (bytes_out) *bytes_out = bytes;
     return rc;
+}
+
+int32_t sh_profile_poll(ShProfileSums* out) {
+    if (out == nullptr) return fail(SH_ERR_INVALID_ARG, "null out");
+    memset(out, 0, sizeof(*out));
+    std::lock_guard<std::mutex> lk(g_prof_mu);
+    size_t kept = 0;
+    for (size_t i = 0; i < g_prof_pending.size(); ++i) {
+        ProfRecord& r = g_prof_pending[i];
+        const cudaError_t q = cudaEventQuery(r.stop);
+        if (q == cudaErrorNotReady) {                  // still running: stays for a later poll
+            g_prof_pending[kept++] = r;
+            continue;
+        }
+        float t = 0.f;
+        if (q == cudaSuccess && cudaEventElapsedTime(&t, r.start, r.stop) == cudaSuccess) {
+            if (r.kind == 0) {
+                out->kernel_ms += t;
+                out->kernel_blocks += 1;
+                out->elements += r.elements;
+                out->kernel_bytes += r.bytes;
+            } else {
+                out->copy_ms += t;
+                out->copies += 1;
+                out->copy_bytes += r.bytes;
+            }
+        } else {
+            (void)cudaGetLastError();
+        }
+        g_prof_free.push_back(r.start);
+        g_prof_free.push_back(r.stop);
+    }
+    g_prof_pending.resize(kept);
+    out->pending = static_cast<int64_t>(kept);
+    return SH_OK;
 }
 
 }  // extern "C"

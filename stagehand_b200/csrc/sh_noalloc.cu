@@ -7,8 +7,12 @@
 // footprint after initialisation.  sh_stream_block_async needs a device staging slab that somebody
 // allocated; this variant brings its own: a fixed array in the library's device image.  Every GPU
 // that loads the library holds SH_NOALLOC_MAX_BYTES of it until the process exits.
-#include "../../include/stagehand_b200.h"
-#include "sq_block_kernel.cuh"
+//
+// When is that memory taken?  CUDA loads a library's device image on a GPU the first time something in it
+// is used there, and the array comes with the image.  sh_init() resolves the array's address, so a process
+// that calls sh_init on each device before it gives its VRAM away has paid for the array by then; a process
+// that skips sh_init pays at this entry point's first call on the device, which can fail for lack of memory.
+#include "sh_common.h"
 
 #include <cstdio>
 #include <cstring>
@@ -51,6 +55,13 @@ int staging_address(void** out) {
 
 }  // namespace
 
+int shc::noalloc_prepare_current_device(char* err, size_t err_len) {
+    void* ptr = nullptr;
+    const int rc = staging_address(&ptr);
+    if (rc != SH_OK && err != nullptr && err_len > 0) snprintf(err, err_len, "%s", g_noalloc_err);
+    return rc;
+}
+
 extern "C" {
 
 int32_t sh_noalloc_last_error(char* buf, int32_t buf_len) {
@@ -91,7 +102,8 @@ int32_t sh_dequant_from_host_noalloc(const ShParamDesc* descs, int32_t n_descs, 
 
     sq::BlockPlan plans[kMaxPlans];
     int n_plans = 0;
-    rc = sq::build_plans(descs, n_descs, staging, packed_bytes, out_dev, out_bytes, out_dtype, plans, &n_plans, nullptr,
+    int64_t elements = 0;
+    rc = sq::build_plans(descs, n_descs, staging, packed_bytes, out_dev, out_bytes, out_dtype, plans, &n_plans, &elements,
                          nullptr, g_noalloc_err, sizeof(g_noalloc_err));
     if (rc != SH_OK) return rc;
 
@@ -107,7 +119,11 @@ int32_t sh_dequant_from_host_noalloc(const ShParamDesc* descs, int32_t n_descs, 
             snprintf(g_noalloc_err, sizeof(g_noalloc_err), "block kernel launch: %s", cudaGetErrorString(e));
             return SH_ERR_CUDA;
         }
+        shc::g_ctr.launches.fetch_add(1, std::memory_order_relaxed);
     }
+    shc::g_ctr.elements.fetch_add(elements, std::memory_order_relaxed);
+    shc::g_ctr.h2d_copies.fetch_add(1, std::memory_order_relaxed);
+    shc::g_ctr.h2d_bytes.fetch_add(static_cast<int64_t>(packed_bytes), std::memory_order_relaxed);
     return SH_OK;
 }
 

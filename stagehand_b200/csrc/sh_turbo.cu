@@ -229,19 +229,19 @@ int32_t sh_turbo_create(uint64_t* engine_out) {
 int32_t sh_turbo_destroy(uint64_t engine) {
     Engine* e = as_engine(engine);
     if (e == nullptr) return SH_OK;
-    if (e->initialized) {
-        cudaStreamSynchronize(e->prefetch);     // shutdown only: the caller has drained already
-        cudaStreamSynchronize(e->evict);
-        for (Block& b : e->blocks) {
-            if (b.host != nullptr) cudaFreeHost(b.host);
-            if (b.moved != nullptr) cudaEventDestroy(b.moved);
-        }
-        for (void* p : e->staging)
-            if (p != nullptr) cudaFree(p);
-        cudaEventDestroy(e->fence);
-        cudaStreamDestroy(e->prefetch);
-        cudaStreamDestroy(e->evict);
+    // Everything that exists is released, whether or not initialize() ran to its end: a failure half-way
+    // (out of page-locked or device memory) leaves streams, events and some buffers behind.
+    if (e->prefetch != nullptr) cudaStreamSynchronize(e->prefetch);     // shutdown only: the caller has drained already
+    if (e->evict != nullptr) cudaStreamSynchronize(e->evict);
+    for (Block& b : e->blocks) {
+        if (b.host != nullptr) cudaFreeHost(b.host);
+        if (b.moved != nullptr) cudaEventDestroy(b.moved);
     }
+    for (void* p : e->staging)
+        if (p != nullptr) cudaFree(p);
+    if (e->fence != nullptr) cudaEventDestroy(e->fence);
+    if (e->prefetch != nullptr) cudaStreamDestroy(e->prefetch);
+    if (e->evict != nullptr) cudaStreamDestroy(e->evict);
     delete e;                                    // GPU slot memory belongs to the caller and is not freed here
     return SH_OK;
 }
@@ -288,6 +288,8 @@ int32_t sh_turbo_initialize(uint64_t engine, int32_t device, int32_t window_size
     Engine* e = as_engine(engine);
     if (e == nullptr) return tfail(SH_ERR_INVALID_ARG, "null engine");
     if (e->initialized) return tfail(SH_ERR_INVALID_ARG, "Already initialized");
+    if (e->prefetch != nullptr || e->evict != nullptr)
+        return tfail(SH_ERR_INVALID_ARG, "an earlier initialize failed part-way; destroy this engine and create a new one");
     if (e->blocks.empty()) return tfail(SH_ERR_INVALID_ARG, "No blocks registered");
     if (window_size < 1) return tfail(SH_ERR_INVALID_ARG, "window_size must be at least 1");
     int rc = cuda_check(cudaSetDevice(device), "cudaSetDevice");

@@ -84,8 +84,14 @@ struct Region {
     CUmemGenericAllocationHandle handle = 0;
     int refcount = 0;
     uint64_t last_access = 0;
-    cudaEvent_t released = nullptr;       // recorded on the user's stream at release
-    bool event_pending = false;
+    // One event per release whose work may still be running: every holder records its own, on its own
+    // stream, so a second release never hides what the first stream still has queued.  Completed events
+    // stay in the list and are recorded again by later releases.
+    struct Release {
+        cudaEvent_t event = nullptr;
+        bool pending = false;
+    };
+    std::vector<Release> releases;
 };
 
 struct Slab {
@@ -116,23 +122,29 @@ struct Allocator {
 
 size_t round_up(size_t v, size_t g) { return (v + g - 1) / g * g; }
 
-bool event_done(Region& r, int timeout_ms) {
-    if (!r.event_pending) return true;
-    const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms);
-    for (;;) {
-        const cudaError_t q = cudaEventQuery(r.released);
+// Non-blocking: true when every release event of the region has completed (or none is pending).
+// A query that fails for any other reason than "not ready" counts as not idle.
+bool region_idle(Region& r) {
+    for (auto& rel : r.releases) {
+        if (!rel.pending) continue;
+        const cudaError_t q = cudaEventQuery(rel.event);
         if (q == cudaSuccess) {
-            r.event_pending = false;
-            return true;
+            rel.pending = false;
+            continue;
         }
-        if (q != cudaErrorNotReady) {
-            (void)cudaGetLastError();
-            return false;
-        }
-        if (std::chrono::steady_clock::now() >= deadline) return false;
-        std::this_thread::sleep_for(std::chrono::microseconds(50));
+        if (q != cudaErrorNotReady) (void)cudaGetLastError();
+        return false;
     }
+    return true;
 }
+
+void destroy_release_events(Region& r) {
+    for (auto& rel : r.releases)
+        if (rel.event != nullptr) cudaEventDestroy(rel.event);
+    r.releases.clear();
+}
+
+constexpr int kReleaseWaitMs = 10000;
 
 int unmap_region(Allocator& a, Slab& s, Region& r) {
     Driver& d = driver();
@@ -147,15 +159,27 @@ int unmap_region(Allocator& a, Slab& s, Region& r) {
     return SH_OK;
 }
 
-// Unmap unreferenced regions (lowest slab priority, then least recently used) until `need` more bytes fit.
-int make_room(Allocator& a, size_t need, int skip_slab, int skip_region) {
+// Unmap unreferenced regions until `need` more bytes fit.  A region is a victim only when nobody holds
+// it AND the work queued before its releases has finished; among those, lowest slab priority first, then
+// least recently used.  Released regions whose work is still running are never waited for while an idle
+// one exists.  When every candidate is still busy, the allocator's mutex is dropped while this thread
+// polls (other callers keep going), for at most kReleaseWaitMs in total; only then SH_ERR_TIMEOUT.
+// `lk` must hold a.mu on entry and holds it on return.  Pointers into a.slabs taken by the caller before
+// the call may be stale afterwards when `*waited` comes back true.
+int make_room(Allocator& a, std::unique_lock<std::mutex>& lk, size_t need, int skip_slab, int skip_region, bool* waited) {
+    const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(kReleaseWaitMs);
     while (a.mapped + need > a.ceiling) {
         Slab* vs = nullptr;
         Region* vr = nullptr;
+        bool busy_candidates = false;
         for (auto& [sid, s] : a.slabs) {
             for (size_t i = 0; i < s.regions.size(); ++i) {
                 Region& r = s.regions[i];
                 if (!r.mapped || r.refcount > 0 || (sid == skip_slab && static_cast<int>(i) == skip_region)) continue;
+                if (!region_idle(r)) {
+                    busy_candidates = true;
+                    continue;
+                }
                 if (vr == nullptr || s.priority < vs->priority ||
                     (s.priority == vs->priority && r.last_access < vr->last_access)) {
                     vs = &s;
@@ -163,22 +187,47 @@ int make_room(Allocator& a, size_t need, int skip_slab, int skip_region) {
                 }
             }
         }
-        if (vr == nullptr)
+        if (vr != nullptr) {
+            const int rc = unmap_region(a, *vs, *vr);
+            if (rc != SH_OK) return rc;
+            a.evictions += 1;
+            continue;
+        }
+        if (!busy_candidates)
             return vfail(SH_ERR_OOM, "VRAM ceiling of %zu bytes reached and no region is evictable (mapped %zu, need %zu)",
                          a.ceiling, a.mapped, need);
-        if (!event_done(*vr, 10000)) return vfail(SH_ERR_TIMEOUT, "released region is still in use on the GPU after 10 s");
-        const int rc = unmap_region(a, *vs, *vr);
-        if (rc != SH_OK) return rc;
-        a.evictions += 1;
+        if (std::chrono::steady_clock::now() >= deadline)
+            return vfail(SH_ERR_TIMEOUT, "every released region is still in use on the GPU after %d ms", kReleaseWaitMs);
+        if (waited != nullptr) *waited = true;
+        lk.unlock();
+        std::this_thread::sleep_for(std::chrono::microseconds(100));
+        lk.lock();
     }
     return SH_OK;
 }
 
-int map_region(Allocator& a, int slab_id, Slab& s, int region_id, Region& r) {
+int find(Allocator& a, int slab, int region, Slab** s_out, Region** r_out);
+
+// Maps (slab_id, region_id).  `lk` holds a.mu; it may be dropped and retaken while room is made, so the
+// region is looked up again afterwards (it may have been destroyed, or mapped by another thread).
+int map_region(Allocator& a, std::unique_lock<std::mutex>& lk, int slab_id, int region_id) {
     Driver& d = driver();
-    if (r.size > a.ceiling) return vfail(SH_ERR_OOM, "region of %zu bytes exceeds the VRAM ceiling of %zu", r.size, a.ceiling);
-    int rc = make_room(a, r.size, slab_id, region_id);
+    Slab* sp = nullptr;
+    Region* rp = nullptr;
+    int rc = find(a, slab_id, region_id, &sp, &rp);
     if (rc != SH_OK) return rc;
+    if (rp->size > a.ceiling)
+        return vfail(SH_ERR_OOM, "region of %zu bytes exceeds the VRAM ceiling of %zu", rp->size, a.ceiling);
+    bool waited = false;
+    rc = make_room(a, lk, rp->size, slab_id, region_id, &waited);
+    if (rc != SH_OK) return rc;
+    if (waited) {
+        rc = find(a, slab_id, region_id, &sp, &rp);
+        if (rc != SH_OK) return rc;
+        if (rp->mapped) return SH_OK;
+    }
+    Slab& s = *sp;
+    Region& r = *rp;
     CUresult e = d.Create(&r.handle, r.size, &a.prop, 0);
     if (e == CUDA_ERROR_OUT_OF_MEMORY) return vfail(SH_ERR_OOM, "cuMemCreate: out of device memory (%zu bytes)", r.size);
     if (e != CUDA_SUCCESS) return vfail(SH_ERR_CUDA, "cuMemCreate failed (%d)", static_cast<int>(e));
@@ -271,9 +320,11 @@ int32_t sh_vmm_destroy(uint64_t allocator) {
         std::lock_guard<std::mutex> lk(a->mu);
         for (auto& [sid, s] : a->slabs) {
             for (auto& r : s.regions) {
-                (void)event_done(r, 10000);
+                const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(kReleaseWaitMs);
+                while (!region_idle(r) && std::chrono::steady_clock::now() < deadline)
+                    std::this_thread::sleep_for(std::chrono::microseconds(100));
                 (void)unmap_region(*a, s, r);
-                if (r.released != nullptr) cudaEventDestroy(r.released);
+                destroy_release_events(r);
             }
             driver().AddressFree(s.base, s.size);
         }
@@ -333,8 +384,8 @@ static void prefetch_loop(Allocator* a) {
         Region* r = nullptr;
         // best effort: a request for something destroyed meanwhile, or one that finds no room, is dropped
         if (find(*a, req.first, req.second, &s, &r) == SH_OK && !r->mapped) {
-            if (map_region(*a, req.first, *s, req.second, *r) != SH_OK) a->prefetch_failures += 1;
-            else r->last_access = ++a->clock;
+            if (map_region(*a, lk, req.first, req.second) != SH_OK) a->prefetch_failures += 1;
+            else if (find(*a, req.first, req.second, &s, &r) == SH_OK) r->last_access = ++a->clock;
         }
         a->worker_busy = false;
         if (a->requests.empty()) a->idle.notify_all();
@@ -371,13 +422,15 @@ int32_t sh_vmm_prefetch_wait(uint64_t allocator, int32_t timeout_ms) {
 int32_t sh_vmm_ensure_resident(uint64_t allocator, int32_t slab, int32_t region, int32_t hold, void** dev_ptr_out) {
     Allocator* a = as_alloc(allocator);
     if (a == nullptr) return vfail(SH_ERR_INVALID_ARG, "null allocator");
-    std::lock_guard<std::mutex> lk(a->mu);
+    std::unique_lock<std::mutex> lk(a->mu);
     Slab* s = nullptr;
     Region* r = nullptr;
     int rc = find(*a, slab, region, &s, &r);
     if (rc != SH_OK) return rc;
     if (!r->mapped) {
-        rc = map_region(*a, slab, *s, region, *r);
+        rc = map_region(*a, lk, slab, region);
+        if (rc != SH_OK) return rc;
+        rc = find(*a, slab, region, &s, &r);       // the lock may have been dropped while room was made
         if (rc != SH_OK) return rc;
     }
     r->last_access = ++a->clock;
@@ -396,15 +449,24 @@ int32_t sh_vmm_release(uint64_t allocator, int32_t slab, int32_t region, uint64_
     if (rc != SH_OK) return rc;
     if (r->refcount <= 0) return vfail(SH_ERR_INVALID_ARG, "region %d of slab %d is not held", region, slab);
     r->refcount -= 1;
-    if (r->released == nullptr && cudaEventCreateWithFlags(&r->released, cudaEventDisableTiming) != cudaSuccess) {
-        (void)cudaGetLastError();
-        return vfail(SH_ERR_CUDA, "cudaEventCreate failed");
+    (void)region_idle(*r);                          // retire completed events so one of them can be reused
+    Region::Release* slot = nullptr;
+    for (auto& rel : r->releases)
+        if (!rel.pending) { slot = &rel; break; }
+    if (slot == nullptr) {
+        Region::Release fresh;
+        if (cudaEventCreateWithFlags(&fresh.event, cudaEventDisableTiming) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return vfail(SH_ERR_CUDA, "cudaEventCreate failed");
+        }
+        r->releases.push_back(fresh);
+        slot = &r->releases.back();
     }
-    if (cudaEventRecord(r->released, reinterpret_cast<cudaStream_t>(static_cast<uintptr_t>(stream))) != cudaSuccess) {
+    if (cudaEventRecord(slot->event, reinterpret_cast<cudaStream_t>(static_cast<uintptr_t>(stream))) != cudaSuccess) {
         (void)cudaGetLastError();
         return vfail(SH_ERR_CUDA, "cudaEventRecord failed");
     }
-    r->event_pending = true;
+    slot->pending = true;
     return SH_OK;
 }
 
@@ -422,26 +484,41 @@ int32_t sh_vmm_set_priority(uint64_t allocator, int32_t slab, uint32_t priority)
 int32_t sh_vmm_set_ceiling(uint64_t allocator, uint64_t ceiling_bytes) {
     Allocator* a = as_alloc(allocator);
     if (a == nullptr || ceiling_bytes == 0) return vfail(SH_ERR_INVALID_ARG, "bad ceiling");
-    std::lock_guard<std::mutex> lk(a->mu);
+    std::unique_lock<std::mutex> lk(a->mu);
     a->ceiling = static_cast<size_t>(ceiling_bytes);
-    return make_room(*a, 0, -1, -1);
+    return make_room(*a, lk, 0, -1, -1, nullptr);
 }
 
 int32_t sh_vmm_destroy_slab(uint64_t allocator, int32_t slab) {
     Allocator* a = as_alloc(allocator);
     if (a == nullptr) return vfail(SH_ERR_INVALID_ARG, "null allocator");
-    std::lock_guard<std::mutex> lk(a->mu);
+    std::unique_lock<std::mutex> lk(a->mu);
+    const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(kReleaseWaitMs);
     Slab* s = nullptr;
-    int rc = find(*a, slab, -1, &s, nullptr);
-    if (rc != SH_OK) return rc;
-    for (const Region& r : s->regions)
-        if (r.refcount > 0) return vfail(SH_ERR_BUSY, "slab %d still has held regions", slab);
-    for (Region& r : s->regions) {
-        if (!event_done(r, 10000)) return vfail(SH_ERR_TIMEOUT, "a region of slab %d is still in use on the GPU", slab);
-        rc = unmap_region(*a, *s, r);
+    // First make sure nothing holds or still uses any region; nothing is torn down before that, so a
+    // BUSY or TIMEOUT answer leaves the slab exactly as it was.  The mutex is dropped between polls.
+    for (;;) {
+        const int rc = find(*a, slab, -1, &s, nullptr);
         if (rc != SH_OK) return rc;
-        if (r.released != nullptr) cudaEventDestroy(r.released);
+        bool idle = true;
+        for (Region& r : s->regions) {
+            if (r.refcount > 0) return vfail(SH_ERR_BUSY, "slab %d still has held regions", slab);
+            idle = region_idle(r) && idle;
+        }
+        if (idle) break;
+        if (std::chrono::steady_clock::now() >= deadline)
+            return vfail(SH_ERR_TIMEOUT, "a region of slab %d is still in use on the GPU", slab);
+        lk.unlock();
+        std::this_thread::sleep_for(std::chrono::microseconds(100));
+        lk.lock();
     }
+    int first_error = SH_OK;
+    for (Region& r : s->regions) {
+        const int rc = unmap_region(*a, *s, r);
+        if (rc != SH_OK && first_error == SH_OK) first_error = rc;
+        destroy_release_events(r);
+    }
+    if (first_error != SH_OK) return first_error;     // regions that did unmap stay unmapped; events are gone and forgotten
     driver().AddressFree(s->base, s->size);
     a->slabs.erase(slab);
     return SH_OK;

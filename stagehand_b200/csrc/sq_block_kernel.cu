@@ -501,6 +501,20 @@ static void close_plan(BlockPlan& plan, uint32_t tiles) {
     }
 }
 
+void rebase_plan(BlockPlan& plan, const void* packed_base, void* out_base) {
+    const ptrdiff_t dp = static_cast<const uint8_t*>(packed_base) - static_cast<const uint8_t*>(kPlanStandInBase);
+    const ptrdiff_t dq = static_cast<uint8_t*>(out_base) - static_cast<uint8_t*>(kPlanStandInBase);
+    for (int i = 0; i < plan.n_desc; ++i) {
+        DescDev& D = plan.d[i];
+        if (D.flags & kFlagRelative) {
+            if (D.src != nullptr) D.src += dp;
+            if (D.scale != nullptr) D.scale = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(D.scale) + dp);
+            if (D.zp != nullptr) D.zp = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(D.zp) + dp);
+        }
+        D.dst += dq;
+    }
+}
+
 int build_plans(const ShParamDesc* descs, int n, const void* packed, size_t packed_bytes, void* out,
                 size_t out_bytes, int out_dtype, BlockPlan* plans_out, int* n_plans_out, int64_t* elements_out,
                 int64_t* traffic_bytes_out, char* err, size_t err_len) {
@@ -530,6 +544,7 @@ int build_plans(const ShParamDesc* descs, int n, const void* packed, size_t pack
         memset(&D, 0, sizeof(D));
         D.flags = u.flags & SH_DESC_PEER_SOURCE;
         const bool absolute = (u.flags & SH_DESC_ABSOLUTE) != 0;
+        if (!absolute && u.kind != SH_KIND_ZERO) D.flags |= kFlagRelative;
         int64_t dst_bytes = 0, n_tiles = 0;
 #define SQ_FAIL(...)                                      \
     do {                                                  \

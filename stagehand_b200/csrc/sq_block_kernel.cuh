@@ -49,6 +49,7 @@ enum Path : int32_t {
 constexpr int kStageMinRows    = 32;    // tiles spanning fewer scale rows read them with plain cached loads
 constexpr uint32_t kFlagDense      = 0x400u;   // source rows are contiguous (ld == cols): vector i of the matrix is at src + 16 i
 constexpr uint32_t kFlagStore32    = 0x200u;   // every 16-weight output vector starts on a 32-byte boundary
+constexpr uint32_t kFlagRelative   = 0x800u;   // host side only: src / scale / zp were derived from the packed base (rebase_plan moves them)
 constexpr uint32_t kFlagBulkScales = 0x100u;   // (bit 0 is SH_DESC_PEER_SOURCE) scale (and zero-point) rows may be fetched with a bulk async copy
 
 struct DescDev {
@@ -87,6 +88,12 @@ constexpr int32_t kStatusBadPath     = 2;   // a descriptor carried an unknown p
 int build_plans(const ShParamDesc* descs, int n, const void* packed, size_t packed_bytes,
                 void* out, size_t out_bytes, int out_dtype, BlockPlan* plans_out, int* n_plans_out,
                 int64_t* elements_out, int64_t* traffic_bytes_out, char* err, size_t err_len);
+
+// Plans can be built once against a stand-in base and moved to the real buffers at every launch: build with
+// packed = out = kPlanStandInBase, then rebase_plan(copy, real_packed, real_out).  Both real bases must be
+// 256-byte aligned, so that every alignment decision taken at build time still holds.
+static void* const kPlanStandInBase = reinterpret_cast<void*>(uintptr_t(1) << 20);
+void rebase_plan(BlockPlan& plan, const void* packed_base, void* out_base);
 
 // Launches one plan on `stream`.
 cudaError_t launch_plan(const BlockPlan& plan, int out_dtype, cudaStream_t stream, int32_t* status_dev);

@@ -33,58 +33,111 @@ class DeviceSlab:
 
 
 class DeviceSlabPool:
-    """Exact-size free lists of output slabs (one list per distinct block size)."""
+    """Exact-size output slabs, recycled.  The memory is torch's; the bookkeeping is the library's.
+
+    Which slab is free, which block holds which slot and the event that guards a slab's reuse live behind
+    the C ABI (``sh_vram_pool_*`` / ``sh_slab_acquire`` / ``sh_slab_release``); this class allocates the
+    slabs through torch -- so the watermarks see them -- hands their addresses to that pool, and keeps the
+    tensors alive.  ``acquire`` orders the writer's stream after the slab's previous readers on the device.
+    """
 
     def __init__(self, device: torch.device | str = "cuda", max_parked_bytes: int | None = None,
                  on_allocation=None, on_trim=None) -> None:
+        import ctypes
+
+        from stagehand_b200 import _native
+
         self._device = torch.device(device)
         self._on_allocation = on_allocation       # called after the allocator-visible total changed
         self._on_trim = on_trim                   # called before parked slabs are dropped (holders of views let go)
-        self._free: dict[int, list[DeviceSlab]] = {}
+        self._native, self._lib = _native, _native.lib()
+        handle = ctypes.c_uint64(0)
+        _native.check(self._lib.sh_vram_pool_create(0, None, None, ctypes.byref(handle)), "sh_vram_pool_create")
+        self._pool = int(handle.value)
+        self._slabs: dict[int, DeviceSlab] = {}   # slot -> slab (keeps the tensor alive)
+        self._free_slots: dict[int, list[int]] = {}   # nbytes -> free slots, mirrored here so the budget reads no C call
         self._parked_bytes = 0
         self._max_parked = max_parked_bytes
-        self._next_id = 0
         self.allocations = 0
         self.reuses = 0
 
-    def acquire(self, nbytes: int) -> DeviceSlab:
-        """A slab of exactly *nbytes*: a parked one if there is any, else a new allocation."""
-        bucket = self._free.get(nbytes)
-        if bucket:
-            slab = bucket.pop()
-            self._parked_bytes -= slab.nbytes
+    def _slot_for(self, block_id: bytes, nbytes: int, writer: int) -> int:
+        import ctypes
+
+        slot = ctypes.c_int32(-1)
+        rc = self._lib.sh_slab_acquire(self._pool, block_id, nbytes, nbytes, writer, ctypes.byref(slot), None)
+        if rc == self._native.SH_ERR_BUSY:
+            return -1
+        self._native.check(rc, "sh_slab_acquire")
+        return int(slot.value)
+
+    def acquire(self, nbytes: int, block_id: str = "", writer_stream=None) -> DeviceSlab:
+        """A slab of exactly *nbytes* for *block_id*: a parked one if there is any, else a new allocation.
+
+        *writer_stream* (default: the current stream) is made to wait, on the device, for whatever read the
+        slab before it was given back.
+        """
+        import ctypes
+
+        from stagehand_b200.events import acquire_event, release_event
+
+        if writer_stream is None:
+            writer_stream = torch.cuda.current_stream(self._device)
+        writer = self._native.stream_handle(writer_stream)
+        name = (block_id or f"anonymous-{self.allocations + self.reuses}").encode()
+        slot = self._slot_for(name, nbytes, writer)
+        if slot >= 0:
+            self._free_slots[nbytes].remove(slot)
+            self._parked_bytes -= nbytes
             self.reuses += 1
-            return slab
+            return self._slabs[slot]
         try:
             tensor = torch.empty(nbytes, dtype=torch.uint8, device=self._device)
         except torch.OutOfMemoryError:
             self.trim()
             tensor = torch.empty(nbytes, dtype=torch.uint8, device=self._device)
         self.allocations += 1
-        self._next_id += 1
         if self._on_allocation is not None:
             self._on_allocation()
-        slab = DeviceSlab(tensor=tensor, nbytes=nbytes, slab_id=self._next_id)
-        if self._device.type == "cuda":
-            # The caching allocator may hand back memory that kernels already queued on the
-            # allocating stream still use; the slab's first writer (another stream) waits for them.
-            from stagehand_b200.events import acquire_event
-
-            slab.last_use = acquire_event().record(torch.cuda.current_stream(self._device))
+        # The caching allocator may hand back memory that kernels already queued on the allocating stream
+        # still use; the slab's first writer (another stream) waits for them.
+        fresh = acquire_event().record(torch.cuda.current_stream(self._device))
+        fresh.block_stream(writer_stream)
+        release_event(fresh)
+        added = ctypes.c_int32(-1)
+        self._native.check(self._lib.sh_vram_pool_add_slab(self._pool, tensor.data_ptr(), nbytes, ctypes.byref(added)),
+                           "sh_vram_pool_add_slab")
+        slab = DeviceSlab(tensor=tensor, nbytes=nbytes, slab_id=int(added.value))
+        self._slabs[slab.slab_id] = slab
+        slot = self._slot_for(name, nbytes, writer)
+        if slot != slab.slab_id:
+            raise RuntimeError(f"slab pool handed out slot {slot} instead of the new slot {slab.slab_id}")
         return slab
 
     def release(self, slab: DeviceSlab, stream: torch.cuda.Stream | None = None) -> None:
         """Park *slab*; readers queued on *stream* (default: current) finish before its next writer starts."""
-        if self._device.type == "cuda":
-            from stagehand_b200.events import acquire_event, release_event
-
-            release_event(slab.last_use)
-            slab.last_use = acquire_event().record(
-                stream if stream is not None else torch.cuda.current_stream(self._device))
+        s = stream if stream is not None else torch.cuda.current_stream(self._device)
+        self._native.check(self._lib.sh_slab_release(self._pool, slab.slab_id, self._native.stream_handle(s)),
+                           "sh_slab_release")
         if self._max_parked is not None and self._parked_bytes + slab.nbytes > self._max_parked:
-            return   # dropped: the tensor goes back to the caching allocator
-        self._free.setdefault(slab.nbytes, []).append(slab)
+            self._drop(slab.slab_id)             # the tensor goes back to the caching allocator
+            return
+        self._free_slots.setdefault(slab.nbytes, []).append(slab.slab_id)
         self._parked_bytes += slab.nbytes
+
+    def _drop(self, slot: int) -> None:
+        # No host wait: the memory returns to torch's allocator, whose next user is ordered behind the stream
+        # the release was recorded on (the stream the slab was allocated and read on).
+        self._native.check(self._lib.sh_vram_pool_remove_slab(self._pool, slot, -1), "sh_vram_pool_remove_slab")
+        self._slabs.pop(slot, None)
+
+    def location(self, block_id: str) -> int:
+        """Slot *block_id* holds, or -1."""
+        import ctypes
+
+        slot = ctypes.c_int32(-1)
+        self._native.check(self._lib.sh_block_location(self._pool, block_id.encode(), ctypes.byref(slot)), "sh_block_location")
+        return int(slot.value)
 
     def reusable_bytes(self) -> int:
         return self._parked_bytes
@@ -93,10 +146,28 @@ class DeviceSlabPool:
         """Give every parked slab back to the allocator."""
         if self._on_trim is not None:
             self._on_trim()
-        self._free.clear()
+        for slots in self._free_slots.values():
+            for slot in slots:
+                self._drop(slot)
+        self._free_slots.clear()
         self._parked_bytes = 0
         if self._on_allocation is not None:
             self._on_allocation()
+
+    def destroy(self) -> None:
+        """Forget the pool behind the ABI (slabs still held keep their memory through their tensors)."""
+        if self._pool:
+            self._lib.sh_vram_pool_destroy(self._pool)
+            self._pool = 0
+            self._slabs.clear()
+            self._free_slots.clear()
+            self._parked_bytes = 0
+
+    def __del__(self) -> None:
+        try:
+            self.destroy()
+        except Exception:
+            pass
 
 
 class StagingRing:
@@ -154,7 +225,9 @@ class VmmDeviceSlabPool:
         self.allocations = 0
         self.reuses = 0
 
-    def acquire(self, nbytes: int) -> DeviceSlab:
+    def acquire(self, nbytes: int, block_id: str = "", writer_stream=None) -> DeviceSlab:
+        """Same call as :meth:`DeviceSlabPool.acquire`; the ordering of the writer is left to the slab's
+        ``last_use`` event, which the streamer waits for."""
         from stagehand_b200.events import acquire_event
 
         bucket = self._free.get(nbytes)

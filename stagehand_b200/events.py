@@ -52,6 +52,13 @@ class Event:
             _native.lib().sh_event_destroy(self.handle)
             self.handle = 0
 
+    def __del__(self) -> None:
+        # an event nobody refers to any more (pooled ones are referred to by the free list)
+        try:
+            self.destroy()
+        except Exception:
+            pass
+
 
 _free: list[Event] = []
 

@@ -95,6 +95,8 @@ class PackedBlockImage:
     dynamic_rows: list[_DynamicRow] = field(default_factory=list)
     _static_split: Any = None
     last_source: dict[str, int] = field(default_factory=dict)   # dynamic row -> data_ptr of the tensor last staged
+    desc_version: int = 0                        # bumped whenever a descriptor's kind or size changes (plans built
+                                                 # from the descriptors, e.g. a registered block, are then stale)
 
     @property
     def out_dtype_code(self) -> int:
@@ -166,8 +168,11 @@ class PackedBlockImage:
                 changed = changed or desc.kind != SH_KIND_ZERO or row.staged_from is not None
                 row.staged_from = None
                 self.last_source.pop(row.name, None)
+                before = (desc.kind, desc.cols)
                 desc.kind = SH_KIND_ZERO
                 desc.cols = row.numel * self.runtime_dtype.itemsize
+                if (desc.kind, desc.cols) != before:
+                    self.desc_version += 1
                 continue
             self.last_source[row.name] = source.data_ptr()
             # inference tensors carry no version counter: they are always restaged
@@ -183,6 +188,7 @@ class PackedBlockImage:
             flat = source.detach().reshape(-1)
             if flat.device.type != "cpu":
                 flat = flat.cpu()
+            before = (desc.kind, desc.cols)
             if flat.dtype == torch.float32 and self.runtime_dtype != torch.float32:
                 desc.kind, desc.cols = SH_KIND_CAST_F32, row.numel
             else:
@@ -196,6 +202,8 @@ class PackedBlockImage:
                         desc.kind, desc.cols = SH_KIND_COPY, row.numel * self.runtime_dtype.itemsize
                 else:
                     desc.kind, desc.cols = SH_KIND_COPY, row.numel * self.runtime_dtype.itemsize
+            if (desc.kind, desc.cols) != before:
+                self.desc_version += 1
             nbytes = flat.numel() * flat.element_size()
             at = row.offset - base_offset   # base_offset = static_bytes when *buffer* holds the dynamic section only
             slot = buffer[at : at + nbytes].view(flat.dtype)

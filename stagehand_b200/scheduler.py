@@ -211,6 +211,11 @@ class StagehandScheduler:
         self._module_mirrors: dict[str, tuple[torch.Tensor, dict[str, torch.Tensor], bool]] = {}   # flat, views, pinned
         self._save_buffers: dict[tuple[str, str, str], torch.Tensor] = {}
         self._pending_saves: dict[str, torch.cuda.Event] = {}
+        self._status_warned = False
+        self._time_blocks = bool(getattr(config, "telemetry_block_timings", False) and config.telemetry_enabled)
+        self._nvtx = bool(getattr(config, "nvtx_ranges", False))
+        self._stall_probes: list[tuple[Any, Any]] = []          # (before, after) timing events on the compute stream
+        self._timing_events: list[Any] = []                     # recycled timing events
 
     # ── step lifecycle ───────────────────────────────────────────────
 
@@ -223,6 +228,8 @@ class StagehandScheduler:
         self._view_cache: dict[tuple[str, int], list[tuple[Any, str, torch.Tensor]]] = {}
         if getattr(self, "_image_plans", None):
             self._image_plans.clear()
+        if getattr(self, "_streamer", None) is not None:
+            self._streamer.forget()          # plans registered with the library were built from the old images
 
     def begin_step(self, step: int) -> None:
         self._current_step = step
@@ -237,7 +244,53 @@ class StagehandScheduler:
         self._reap_deferred_slabs()
         self._reconcile_file_backed_grads()
         self._await_saves()              # the caller's optimiser reads parameters and gradients next
+        self._check_kernel_status()
+        self._harvest_device_times()
         self._telemetry.end_step()
+
+    def _timing_event(self) -> Any:
+        from stagehand_b200.events import Event
+
+        return self._timing_events.pop() if self._timing_events else Event(True)
+
+    def _harvest_device_times(self) -> None:
+        """Fill the step's device-side times from events that have completed; nothing here waits."""
+        if not self._time_blocks or self._streamer is None:
+            return
+        import ctypes
+
+        from stagehand_b200 import _native
+
+        sums = _native.ShProfileSums()
+        _native.check(_native.lib().sh_profile_poll(ctypes.byref(sums)), "sh_profile_poll")
+        exposed = 0.0
+        keep = []
+        for before, after in self._stall_probes:
+            if after.done():
+                exposed += before.elapsed_ms(after)
+                self._timing_events += [before, after]
+            else:
+                keep.append((before, after))
+        self._stall_probes = keep
+        self._telemetry.record_device_times(copy_ms=float(sums.copy_ms), dequant_ms=float(sums.kernel_ms),
+                                            exposed_stall_ms=exposed, timed_blocks=int(sums.kernel_blocks))
+
+    def _check_kernel_status(self) -> None:
+        """Look at the block kernel's status word once per step, without waiting for the GPU.
+
+        Bit 2 means a descriptor was skipped on the device, i.e. some parameter bytes in a slab are
+        stale: that is an error.  Bit 1 (a scale fetch timed out and plain loads were used; the
+        results are correct) is logged once.
+        """
+        if self._streamer is None:
+            return
+        bits = self._streamer.poll_status()
+        if bits & 2:
+            raise TransferError("the block kernel skipped a descriptor it could not execute (device status bit 2): "
+                                "a parameter of a streamed block was not written")
+        if bits & 1 and not self._status_warned:
+            self._status_warned = True
+            log.warning("block kernel: a bulk scale fetch timed out and fell back to plain loads (results are correct)")
 
     def enter_backward_phase(self) -> None:
         self._backward_phase = True
@@ -361,6 +414,9 @@ class StagehandScheduler:
                 self._device_pool.close()
             else:
                 self._device_pool.trim()
+                self._device_pool.destroy()
+        if self._streamer is not None:
+            self._streamer.close()
         self._image_plans.clear()
         for packed in self._packed_files.values():
             packed.close()
@@ -444,7 +500,18 @@ class StagehandScheduler:
             from stagehand_b200.events import release_event
 
             done = pending.ready.done()
-            pending.ready.block_stream(torch.cuda.current_stream())
+            compute = torch.cuda.current_stream()
+            if self._nvtx:
+                torch.cuda.nvtx.range_push(f"stagehand.wait {block_id}")
+            if self._time_blocks and not done:
+                # how long the compute stream sits at the wait: two timing events around it, read at step end
+                before, after = self._timing_event().record(compute), self._timing_event()
+                pending.ready.block_stream(compute)
+                self._stall_probes.append((before, after.record(compute)))
+            else:
+                pending.ready.block_stream(compute)
+            if self._nvtx:
+                torch.cuda.nvtx.range_pop()
             release_event(pending.ready)
             if pending.host_slab is not None:
                 self._deferred_slabs.append((pending.copied, pending.host_slab))
@@ -600,6 +667,10 @@ class StagehandScheduler:
         if hasattr(self._budget, "set_reusable_bytes_source"):
             self._budget.set_reusable_bytes_source(self._device_pool.reusable_bytes)
         self._image_store = ImageStore(self._image_cache_budget(), pinned=True)
+        if self._time_blocks:
+            from stagehand_b200 import _native
+
+            _native.check(_native.lib().sh_profile_enable(1), "sh_profile_enable")
         # one staging ring sized for the largest image of the registry
         largest = 0
         largest_dyn = 0
@@ -709,11 +780,18 @@ class StagehandScheduler:
                 res.host_slab = (image, slab)
             self._residency.transition(block_id, BlockState.HOST_STAGED)
         image, slab = res.host_slab if res.host_slab is not None else (None, None)
-        out_slab = self._device_pool.acquire(entry.size_bytes)
-        if device_src is None:
-            ticket = self._streamer.submit_from_host(plan, image, out_slab)
-        else:
-            ticket = self._streamer.submit_from_device(plan, device_src, self._device_source_fused, image, out_slab)
+        out_slab = self._device_pool.acquire(entry.size_bytes, block_id, self._streamer.dequant_stream)
+        if self._nvtx:
+            kind = "host" if device_src is None else ("gather" if getattr(device_src, "pieces", None) else "device")
+            torch.cuda.nvtx.range_push(f"stagehand.load {block_id} [{kind}]")
+        try:
+            if device_src is None:
+                ticket = self._streamer.submit_from_host(plan, image, out_slab)
+            else:
+                ticket = self._streamer.submit_from_device(plan, device_src, self._device_source_fused, image, out_slab)
+        finally:
+            if self._nvtx:
+                torch.cuda.nvtx.range_pop()
         ticket.host_slab = slab
         res.host_slab = None
         res.device_slab = out_slab
@@ -847,7 +925,7 @@ class StagehandScheduler:
         layout = _build_param_layout(module, entry.dtype)
         flat = self._module_mirror(block_id, entry, module, layout)
         res.param_layout = layout
-        out_slab = self._device_pool.acquire(entry.size_bytes)
+        out_slab = self._device_pool.acquire(entry.size_bytes, block_id, self._streamer.copy_stream)
         ticket = self._streamer.submit_plain(block_id, flat.data_ptr(), entry.size_bytes, out_slab)
         res.device_slab = out_slab
         res.gpu_tensor = out_slab.tensor[: entry.size_bytes].view(entry.dtype)

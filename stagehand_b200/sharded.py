@@ -10,8 +10,11 @@ static section of every block's packed image can live in device memory instead:
   dequant in one kernel) or pull it into a local staging slab with a copy engine first;
 * ``layout="striped"``: the rows of every weight matrix are cut into ``world`` stripes, one
   per rank, so that a block load reads 1/world of its bytes from every GPU -- NVLink egress
-  stays balanced even when all ranks want the same block at the same moment.  Always fused:
-  the consumer's descriptors carry absolute addresses into the ranks' arenas.
+  stays balanced even when all ranks want the same block at the same moment.  A rank's share
+  of one block is one contiguous chunk of its arena.  Delivery is either *fused* (the
+  consumer's descriptors carry absolute addresses into the ranks' arenas and the block kernel
+  loads over NVLink itself) or *gathered* (``gather=True``: one copy-engine pull per owner
+  into the local staging slab, then the kernel on local memory only -- no SM waits on NVLink).
 
 Arenas are allocated with ``sh_device_alloc`` and exported with CUDA IPC; the 64-byte handles
 are exchanged once with ``all_gather_object``.  There is no data-path collective: each rank
@@ -31,7 +34,7 @@ from stagehand_b200._native import (SH_DESC_ABSOLUTE, SH_DESC_PEER_SOURCE, SH_KI
                                     ShParamDesc)
 from stagehand_b200.errors import TransferError
 
-__all__ = ["ShardPlan", "plan_shards", "StripePiece", "StripeDesc", "BlockStripes", "plan_block_stripes",
+__all__ = ["ShardPlan", "plan_shards", "StripePiece", "StripeDesc", "BlockStripes", "plan_block_stripes", "plan_gather",
            "DeviceImageStore", "close_arenas_in_order", "park_images_in_hbm", "shard_images_over_ranks"]
 
 _ALIGN = 4096
@@ -105,6 +108,29 @@ class StripeDesc:
 class BlockStripes:
     pieces: list[StripePiece] = field(default_factory=list)
     descs: list[StripeDesc] = field(default_factory=list)
+    chunks: dict[int, tuple[int, int]] = field(default_factory=dict)   # rank -> [start, end) of this block in its arena
+
+
+def plan_gather(chunks: dict[int, tuple[int, int]], rank: int, world: int) -> tuple[dict[int, int], int, list[tuple[int, int, int, int]]]:
+    """How *rank* pulls one block's remote chunks into its staging slab.
+
+    Returns ``(staging offset of each remote rank's chunk, staging bytes, copies)`` where a copy is
+    ``(owner, arena offset, staging offset, bytes)``.  Chunks keep their 4 KiB alignment, so every
+    address keeps the alignment it has in the arena.  Copies are ordered rank+1, rank+2, ...: ranks that
+    run in step then pull from different owners at any one moment.
+    """
+    offsets: dict[int, int] = {}
+    copies: list[tuple[int, int, int, int]] = []
+    cursor = 0
+    for step in range(1, world):
+        owner = (rank + step) % world
+        start, end = chunks.get(owner, (0, 0))
+        if end <= start:
+            continue
+        offsets[owner] = cursor
+        copies.append((owner, start, cursor, end - start))
+        cursor = _up(cursor + (end - start), _ALIGN)
+    return offsets, cursor, copies
 
 
 def stripe_bounds(rows: int, world: int) -> list[int]:
@@ -124,6 +150,7 @@ def plan_block_stripes(static_descs: Sequence[Any], itemsize: int, world: int, h
     out = BlockStripes()
     for r in range(world):
         arena_cursor[r] = _up(arena_cursor[r], _ALIGN)
+    starts = list(arena_cursor)
 
     def place(rank: int, full_off: int, nbytes: int, align: int, reserve: int | None = None) -> int:
         at = _up(arena_cursor[rank], align)
@@ -154,6 +181,7 @@ def plan_block_stripes(static_descs: Sequence[Any], itemsize: int, world: int, h
             out.descs.append(StripeDesc(int(d.kind), home_rank, src, 0, -1, int(d.dst_off), 1, int(d.cols), 0))
         for made in out.descs[n_before:]:
             made.weight = weight
+    out.chunks = {r: (starts[r], arena_cursor[r]) for r in range(world) if arena_cursor[r] > starts[r]}
     return out
 
 
@@ -185,7 +213,8 @@ class DeviceImageStore:
     """
 
     def __init__(self, runtime: Any, rank: int = 0, world: int = 1, layout: str = "owner", fused: bool = True,
-                 group: Any = None, emulate_world: int = 0, peer_ctas_per_sm: int | None = None) -> None:
+                 group: Any = None, emulate_world: int = 0, peer_ctas_per_sm: int | None = None,
+                 gather: bool = False) -> None:
         if not torch.cuda.is_available():
             raise TransferError("device-resident images need a CUDA device")
         if peer_ctas_per_sm is not None:
@@ -200,6 +229,7 @@ class DeviceImageStore:
         if self._emulated:
             rank, world = 0, emulate_world
         self.rank, self.world, self.fused, self.layout = rank, world, fused, layout
+        self.gather = bool(gather) and layout == "striped" and world > 1
         self._runtime = runtime
         sched = runtime._scheduler
         sched._ensure_int8_path()
@@ -227,10 +257,11 @@ class DeviceImageStore:
         if not self._emulated:
             self._exchange_handles(group)
 
-        sched.set_device_sources(self._sources(), fused=fused or layout == "striped")
-        largest_dyn = max((p.total_bytes - p.static_bytes for p in self._plans.values()), default=0)
+        sources = self._sources()
+        sched.set_device_sources(sources, fused=fused or layout == "striped")
         largest = max((p.total_bytes for p in self._plans.values()), default=_ALIGN)
-        sched._streamer.ensure_staging(largest, largest_dyn)
+        largest = max([largest] + [src.span_bytes for src in sources.values() if src.pieces])
+        sched._streamer.ensure_staging(largest)
 
     # ── planning ─────────────────────────────────────────────────────
 
@@ -312,17 +343,29 @@ class DeviceImageStore:
                 groups.setdefault(d.weight, []).append(d)
             rotated = [d for _w, ds in sorted(groups.items())
                        for d in sorted(ds, key=lambda d: (d.rank - self.rank - 1) % self.world)]
+            staged_at, staging_bytes, copies = plan_gather(bs.chunks, self.rank, self.world) if self.gather else ({}, 0, [])
             for d in rotated:
-                base = self._arenas.get(d.rank, 0)
-                flags = 0 if d.kind == SH_KIND_ZERO else SH_DESC_ABSOLUTE | (SH_DESC_PEER_SOURCE if d.rank != self.rank else 0)
+                if d.kind == SH_KIND_ZERO:
+                    base, flags = 0, 0
+                elif self.gather and d.rank != self.rank:
+                    # pulled into the staging slab first: an offset into that slab, read with local loads
+                    base, flags = staged_at[d.rank] - bs.chunks[d.rank][0], 0
+                else:
+                    base = self._arenas.get(d.rank, 0)
+                    flags = SH_DESC_ABSOLUTE | (SH_DESC_PEER_SOURCE if d.rank != self.rank else 0)
+                sourced = d.kind != SH_KIND_ZERO
                 rows.append(ShParamDesc(
-                    kind=d.kind, flags=flags, src_off=base + d.src_off if flags else 0,
+                    kind=d.kind, flags=flags, src_off=base + d.src_off if sourced else 0,
                     scale_off=base + d.scale_off if d.kind == SH_KIND_DEQUANT_I8 else 0,
                     zp_off=(base + d.zp_off) if d.zp_off >= 0 else -1, dst_off=d.dst_off, rows=d.rows, cols=d.cols, ld=d.ld))
             remote_bytes = sum(p.nbytes for p in bs.pieces if p.rank != self.rank)
+            pieces = [(self._arenas[owner] + at, staged, nbytes) for owner, at, staged, nbytes in copies] or None
+            if pieces:
+                remote_bytes = sum(nbytes for _s, _o, nbytes in pieces)     # whole chunks travel, padding included
             sources[block_id] = DeviceSource(ptr=self._arenas[self.rank], is_peer=False, descs=_native.make_descs(rows),
-                                             n_descs=len(rows), span_bytes=max(self.arena_bytes[self.rank], _ALIGN),
-                                             peer_bytes=remote_bytes)
+                                             n_descs=len(rows),
+                                             span_bytes=staging_bytes if pieces else max(self.arena_bytes[self.rank], _ALIGN),
+                                             peer_bytes=remote_bytes, pieces=pieces)
         return sources
 
     def resident_bytes(self) -> int:
@@ -371,9 +414,10 @@ def park_images_in_hbm(runtime: Any, fused: bool = True) -> DeviceImageStore:
     return DeviceImageStore(runtime, rank=0, world=1, fused=fused)
 
 
-def shard_images_over_ranks(runtime: Any, fused: bool = True, layout: str = "striped", group: Any = None) -> DeviceImageStore:
+def shard_images_over_ranks(runtime: Any, fused: bool = True, layout: str = "striped", group: Any = None,
+                            gather: bool = False) -> DeviceImageStore:
     """One process per GPU: shard the INT8 images over the ranks of *group* (default: the world group)."""
     import torch.distributed as dist
 
     return DeviceImageStore(runtime, rank=dist.get_rank(group), world=dist.get_world_size(group), layout=layout,
-                            fused=fused, group=group)
+                            fused=fused, group=group, gather=gather)

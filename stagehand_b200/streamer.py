@@ -25,6 +25,7 @@ import torch
 from stagehand_b200 import _native
 from stagehand_b200.device_pool import DeviceSlab, StagingRing
 from stagehand_b200.errors import StagehandOOMError, TransferError
+from stagehand_b200._native import ShParamDesc
 from stagehand_b200.events import Event, acquire_event, release_event, stream_handle
 from stagehand_b200.packed import PackedBlockImage
 
@@ -115,15 +116,19 @@ class DeviceSource:
 
     Either one contiguous image at *ptr* (this GPU's HBM, or a peer's when *is_peer*), expanded with the
     block's own descriptors, or -- when *descs* is given -- a set of row stripes spread over several GPUs'
-    arenas, described by absolute-address descriptors built once for this consumer.
+    arenas, described by descriptors built once for this consumer.  With *pieces* the remote stripes are
+    first pulled into the local staging slab by copy engines (one copy per owner) and the descriptors of
+    those stripes are offsets into that slab; without, the descriptors carry absolute addresses and the
+    block kernel reads the arenas in place.
     """
 
     ptr: int
     is_peer: bool = False
-    descs: Any = None             # ctypes array of ShParamDesc with SH_DESC_ABSOLUTE set
+    descs: Any = None             # ctypes array of ShParamDesc
     n_descs: int = 0
-    span_bytes: int = 0           # bytes addressable from ptr (bounds for non-absolute descriptors)
+    span_bytes: int = 0           # bytes addressable through offset (non-absolute) descriptors
     peer_bytes: int = 0           # bytes this consumer reads from other GPUs per load
+    pieces: Any = None            # list of (source address, offset in the staging slab, bytes)
 
 
 @dataclass
@@ -139,8 +144,32 @@ class StreamTicket:
     host_slab: Any = None         # pool slab to give back once `copied` is done (uncached images)
 
 
+@dataclass
+class _Registered:
+    """A block registered with the library (``sh_block_register``) and what it was built from."""
+
+    handle: int
+    stamp: tuple                  # identity of the descriptors / source the plans were built from
+    launches: int
+    keepalive: Any = None
+
+
+@dataclass
+class _DynResident:
+    """Device-resident copy of a block's dynamic section (module-owned parameters), for device-sourced loads."""
+
+    buffer: torch.Tensor
+    last_read: Event              # permanent; recorded after every kernel that read the buffer
+    read_once: bool = False
+
+
 class Int8BlockStreamer:
-    """Owns the copy stream, the dequant stream, the staging ring and the device status word."""
+    """Owns the copy stream(s), the dequant stream, the staging ring and the device status word.
+
+    Every block is registered with the library once (descriptors validated, launch plans built); a load is
+    then one ``sh_block_load`` call that queues the copy, the ordering between the streams, the block
+    kernel and the events.
+    """
 
     def __init__(self, device: torch.device, copy_stream: torch.cuda.Stream | None, n_staging: int,
                  dequant_priority: int = -1) -> None:
@@ -148,14 +177,16 @@ class Int8BlockStreamer:
         lib = _native.lib()
         _native.check(lib.sh_init(device.index if device.index is not None else torch.cuda.current_device()), "sh_init")
         self.copy_stream = copy_stream if copy_stream is not None else torch.cuda.Stream(device=device, priority=-1)
+        self.copy_stream2: torch.cuda.Stream | None = None      # second copy engine for gathers, made on first use
         self.dequant_stream = torch.cuda.Stream(device=device, priority=dequant_priority)
         self._n_staging = max(1, n_staging)
         self._ring: StagingRing | None = None
-        self._dyn_ring: StagingRing | None = None
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self._lib = lib
-        # device-resident copies of blocks' dynamic sections: block_id -> [tensor, merged descs, n, last_read event]
-        self._dyn_resident: dict[str, list] = {}
+        self._registered: dict[tuple[str, str], _Registered] = {}
+        self._dyn_resident: dict[str, _DynResident] = {}
+        self._args = _native.ShBlockLoad()
+        self._status_bits = 0
 
     # ── staging ──────────────────────────────────────────────────────
 
@@ -165,50 +196,99 @@ class Int8BlockStreamer:
         if self._ring is None or self._ring.slab_bytes < need:
             self._ring = None
             self._ring = StagingRing(self._n_staging, need, self.device)
-        if max_dynamic_bytes > 0:
-            need_dyn = -(-max_dynamic_bytes // 4096) * 4096
-            if self._dyn_ring is None or self._dyn_ring.slab_bytes < need_dyn:
-                self._dyn_ring = StagingRing(self._n_staging, need_dyn, self.device)
 
     def staging_bytes(self) -> int:
-        total = self._ring.total_bytes() if self._ring is not None else 0
-        return total + (self._dyn_ring.total_bytes() if self._dyn_ring is not None else 0)
+        return self._ring.total_bytes() if self._ring is not None else 0
 
-    def _take_staging(self, ring: StagingRing, nbytes: int) -> DeviceSlab:
-        if nbytes > ring.slab_bytes:
-            raise StagehandOOMError(f"packed image of {nbytes} bytes exceeds the staging slab ({ring.slab_bytes} bytes)")
-        slab = ring.next()
-        if slab.last_use is not None:
-            slab.last_use.block_stream(self.copy_stream)    # previous image in this slab fully expanded
-        return slab
+    def _take_staging(self, nbytes: int) -> tuple[DeviceSlab, int]:
+        """Next slab of the ring and the event (0: none yet) its next writer has to wait for.
 
-    def _order_output(self, out_slab: DeviceSlab) -> None:
+        A staging slab owns one event for good: it is recorded after every kernel that reads the slab and
+        waited for by the next copy into it (a wait takes the event as recorded at the time of the call).
+        """
+        if self._ring is None:
+            self.ensure_staging(nbytes)
+        if nbytes > self._ring.slab_bytes:
+            raise StagehandOOMError(f"packed image of {nbytes} bytes exceeds the staging slab ({self._ring.slab_bytes} bytes)")
+        slab = self._ring.next()
+        if slab.last_use is None:
+            slab.last_use = Event(False)
+            return slab, 0
+        return slab, slab.last_use.handle
+
+    # ── registration ─────────────────────────────────────────────────
+
+    def _register(self, key: tuple[str, str], stamp: tuple, descs: Any, n_descs: int, packed_bytes: int, out_bytes: int,
+                  dtype_code: int, pieces: Any = None, keepalive: Any = None) -> _Registered:
+        hit = self._registered.get(key)
+        if hit is not None and hit.stamp == stamp:
+            return hit
+        if hit is not None:
+            self._lib.sh_block_unregister(hit.handle)
+            del self._registered[key]
+        out = ctypes.c_uint64(0)
+        _native.check(self._lib.sh_block_register(descs, n_descs, packed_bytes, out_bytes, dtype_code, ctypes.byref(out)),
+                      f"sh_block_register({key[0]})")
+        reg = _Registered(int(out.value), stamp, -(-n_descs // _native.MAX_DESCS_PER_LAUNCH), keepalive)
+        if pieces:
+            arr = (_native.ShGatherPiece * len(pieces))()
+            for i, (src, off, nbytes) in enumerate(pieces):
+                arr[i].src_dev, arr[i].staging_off, arr[i].bytes = int(src), int(off), int(nbytes)
+            rc = self._lib.sh_block_set_gather(reg.handle, arr, len(pieces))
+            if rc != _native.SH_OK:
+                self._lib.sh_block_unregister(reg.handle)
+                _native.check(rc, f"sh_block_set_gather({key[0]})")
+        self._registered[key] = reg
+        return reg
+
+    def forget(self, block_id: str | None = None) -> None:
+        """Drop the registrations of *block_id* (or of every block): its descriptors are about to change."""
+        for key in [k for k in self._registered if block_id is None or k[0] == block_id]:
+            self._lib.sh_block_unregister(self._registered.pop(key).handle)
+        if block_id is None:
+            self._dyn_resident.clear()
+        else:
+            self._dyn_resident.pop(block_id, None)
+
+    def _load(self, reg: _Registered, what: str, *, src: int, kind: int, staging: int, out_slab: DeviceSlab,
+              staging_free: int = 0, src_ready: int = 0, copied: int = 0, copied2: int = 0, ready: int = 0,
+              ready2: int = 0, ready3: int = 0, two_copy_streams: bool = False) -> None:
+        a = self._args
+        a.src, a.staging_dev, a.out_dev = src or None, staging or None, out_slab.tensor.data_ptr()
+        a.status_dev = self.status.data_ptr()
+        a.copy_stream = stream_handle(self.copy_stream)
+        a.copy_stream2 = stream_handle(self.copy_stream2) if two_copy_streams and self.copy_stream2 is not None else 0
+        a.dequant_stream = stream_handle(self.dequant_stream)
+        a.ev_staging_free, a.ev_src_ready = staging_free, src_ready
+        a.ev_out_free = 0
+        if out_slab.last_use is not None:          # slabs of a pool that leaves the ordering to the writer
+            a.ev_out_free = out_slab.last_use.handle
+        a.ev_copied, a.ev_copied2, a.ev_ready, a.ev_ready2, a.ev_ready3 = copied, copied2, ready, ready2, ready3
+        a.src_kind = kind
+        rc = self._lib.sh_block_load(reg.handle, ctypes.byref(a))
         if out_slab.last_use is not None:
-            out_slab.last_use.block_stream(self.dequant_stream)   # previous readers of the slab are done
             release_event(out_slab.last_use)
             out_slab.last_use = None
+        _native.check(rc, what)
 
     # ── submissions ──────────────────────────────────────────────────
 
     def submit_from_host(self, image: PackedBlockImage, host: HostImage, out_slab: DeviceSlab) -> StreamTicket:
         """Host-resident image: one DMA over the host link, one block kernel."""
-        if self._ring is None:
-            self.ensure_staging(image.total_bytes)
-        staging = self._take_staging(self._ring, image.total_bytes)
-        self._order_output(out_slab)
+        staging, staging_free = self._take_staging(image.total_bytes)
         copied, ready = acquire_event(), acquire_event()
-        rc = self._lib.sh_stream_block_async(
-            image.descs, image.n_descs, host.buffer.data_ptr(), image.total_bytes, staging.tensor.data_ptr(),
-            out_slab.tensor.data_ptr(), image.out_bytes, image.out_dtype_code,
-            stream_handle(self.copy_stream), stream_handle(self.dequant_stream), copied.handle, ready.handle,
-            self.status.data_ptr())
-        _native.check(rc, f"sh_stream_block_async({image.block_id})")
-        release_event(staging.last_use)
-        staging.last_use = acquire_event().record(self.dequant_stream)
-        release_event(host.last_copy)
-        host.last_copy = acquire_event().record(self.copy_stream)   # the ticket owns `copied`; the image its own
-        launches = -(-image.n_descs // _native.MAX_DESCS_PER_LAUNCH)
-        return StreamTicket(image.block_id, ready, copied, link_bytes=image.total_bytes, launches=launches)
+        if image.n_descs == 0:
+            ready.record(self.dequant_stream)
+            return StreamTicket(image.block_id, ready, copied.record(self.copy_stream))
+        reg = self._register((image.block_id, "host"), (id(image), image.desc_version), image.descs, image.n_descs,
+                             image.total_bytes, image.out_bytes, image.out_dtype_code, keepalive=image)
+        if host.last_copy is None:
+            host.last_copy = Event(False)           # the image's own, for good (see _take_staging)
+        self._load(reg, f"sh_block_load({image.block_id})", src=host.buffer.data_ptr(), kind=_native.SH_SRC_HOST,
+                   staging=staging.tensor.data_ptr(), out_slab=out_slab, staging_free=staging_free,
+                   copied=copied.handle, copied2=host.last_copy.handle, ready=ready.handle,
+                   ready2=staging.last_use.handle)
+        return StreamTicket(image.block_id, ready, copied, link_bytes=image.total_bytes, launches=reg.launches)
 
     def submit_plain(self, block_id: str, host_ptr: int, nbytes: int, out_slab: DeviceSlab) -> StreamTicket:
         """A block already in the runtime dtype in page-locked memory: one DMA straight into its slab, no kernel."""
@@ -223,135 +303,116 @@ class Int8BlockStreamer:
 
     def submit_from_device(self, image: PackedBlockImage, source: DeviceSource, fused: bool,
                            dynamic_host: HostImage | None, out_slab: DeviceSlab) -> StreamTicket:
-        """Image whose static section is resident in HBM (this GPU's, or a peer's over NVLink).
+        """Image whose static section is resident in HBM (this GPU's, or peers' over NVLink).
 
-        ``fused=True``: the block kernel reads the INT8 rows straight from *src_ptr*
-        (plain peer loads when it is another GPU's memory) -- gather and dequant in
-        one kernel, no staging copy.  ``fused=False``: a copy-engine pull into the
-        local staging slab first, then the kernel.  The dynamic section (live
-        module-owned parameters), if any, always comes from local host memory
-        (*dynamic_host* holds that section only).
+        ``fused=True``: the block kernel reads the INT8 rows where they are (plain peer loads when that is
+        another GPU's memory) -- gather and dequant in one kernel, no staging copy.  ``fused=False``, or a
+        source that names gather pieces: copy engines pull the bytes into the local staging slab first and
+        the kernel reads local memory only.  The dynamic section (live module-owned parameters), if any,
+        comes from local host memory (*dynamic_host* holds that section only): it is kept in a small device
+        buffer, copied again only when the host staged something new, and its descriptors ride in the same
+        launch as the static ones.
         """
         static_descs, n_static, dyn_descs, n_dyn = image.split_descs()
-        src_ptr, src_is_peer = source.ptr, source.is_peer
-        static_bytes = image.static_bytes
-        self._order_output(out_slab)
-        copied: Event | None = None
-        peer_bytes = 0
-        launches = 0
-        dq = stream_handle(self.dequant_stream)
+        pieces = None
         if source.descs is not None:
-            # striped over several arenas: the consumer's absolute-address descriptors, always fused
-            static_descs, n_static = source.descs, source.n_descs
-            packed_ptr, static_bytes, peer_bytes, fused = src_ptr, max(source.span_bytes, 1), source.peer_bytes, True
-        elif fused:
-            if src_is_peer:
-                for i in range(n_static):
-                    static_descs[i].flags |= _native.SH_DESC_PEER_SOURCE
-            packed_ptr = src_ptr
-            peer_bytes = image.static_bytes if src_is_peer else 0
+            static_descs, n_static, span = source.descs, source.n_descs, max(source.span_bytes, 1)
+            pieces, peer_bytes = source.pieces, source.peer_bytes
         else:
-            if self._ring is None:
-                self.ensure_staging(image.total_bytes)
-            staging = self._take_staging(self._ring, image.static_bytes)
-            _native.check(self._lib.sh_pull_block_async(staging.tensor.data_ptr(), src_ptr, image.static_bytes,
-                                                        stream_handle(self.copy_stream)), "sh_pull_block_async")
-            copied = acquire_event().record(self.copy_stream)
-            copied.block_stream(self.dequant_stream)
-            packed_ptr = staging.tensor.data_ptr()
-            peer_bytes = image.static_bytes if src_is_peer else 0
-        if fused and n_dyn:
-            return self._submit_merged(image, source, static_descs, n_static, dyn_descs, n_dyn, packed_ptr, static_bytes,
-                                       peer_bytes, dynamic_host, out_slab)
-        if n_static:
-            _native.check(self._lib.sh_dequant_block_async(
-                static_descs, n_static, packed_ptr, static_bytes, out_slab.tensor.data_ptr(), image.out_bytes,
-                image.out_dtype_code, dq, self.status.data_ptr()), f"sh_dequant_block_async({image.block_id})")
-            launches += -(-n_static // _native.MAX_DESCS_PER_LAUNCH)
-        if not fused:
-            release_event(staging.last_use)
-            staging.last_use = acquire_event().record(self.dequant_stream)
-        link_bytes = 0
+            span = max(image.static_bytes, 1)
+            peer_bytes = image.static_bytes if source.is_peer else 0
+            if not fused:
+                pieces = [(source.ptr, 0, image.static_bytes)] if image.static_bytes else None
+        ready = acquire_event()
+        if n_static + n_dyn == 0:
+            return StreamTicket(image.block_id, ready.record(self.dequant_stream), None)
+
+        link_bytes, src_ready, ready3 = 0, 0, 0
+        dyn = None
         if n_dyn:
             if dynamic_host is None:
                 raise TransferError(f"block {image.block_id!r} has module-owned parameters but no dynamic image")
             dyn_bytes = image.total_bytes - image.static_bytes
-            if self._dyn_ring is None or self._dyn_ring.slab_bytes < dyn_bytes:
-                self.ensure_staging(self._ring.slab_bytes if self._ring else 4096, dyn_bytes)
-            dyn_stage = self._take_staging(self._dyn_ring, dyn_bytes)
-            dyn_copied = acquire_event()
-            dyn_ready = acquire_event()
-            _native.check(self._lib.sh_stream_block_async(
-                dyn_descs, n_dyn, dynamic_host.buffer.data_ptr(), dyn_bytes,
-                dyn_stage.tensor.data_ptr(), out_slab.tensor.data_ptr(), image.out_bytes, image.out_dtype_code,
-                stream_handle(self.copy_stream), dq, dyn_copied.handle, dyn_ready.handle, self.status.data_ptr()),
-                f"dynamic section of {image.block_id}")
-            release_event(dyn_stage.last_use)
-            dyn_stage.last_use = dyn_ready
-            release_event(dynamic_host.last_copy)
-            dynamic_host.last_copy = dyn_copied
-            link_bytes = dyn_bytes
-            launches += -(-n_dyn // _native.MAX_DESCS_PER_LAUNCH)
-        ready = acquire_event().record(self.dequant_stream)
-        return StreamTicket(image.block_id, ready, copied, link_bytes=link_bytes, peer_bytes=peer_bytes,
-                            launches=launches)
-
-    def _submit_merged(self, image: PackedBlockImage, source: DeviceSource, static_descs: Any, n_static: int,
-                       dyn_descs: Any, n_dyn: int, packed_ptr: int, static_bytes: int, peer_bytes: int,
-                       dynamic_host: HostImage | None, out_slab: DeviceSlab) -> StreamTicket:
-        """Fused path with module-owned parameters: ONE launch for the whole block.
-
-        The block's dynamic section is kept resident in a small device buffer and re-copied only when
-        the host staged something new; its descriptors carry that buffer's absolute address and ride in
-        the same launch as the static ones.
-        """
-        if dynamic_host is None:
-            raise TransferError(f"block {image.block_id!r} has module-owned parameters but no dynamic image")
-        dyn_bytes = image.total_bytes - image.static_bytes
-        entry = self._dyn_resident.get(image.block_id)
-        link_bytes = 0
-        if entry is None or dynamic_host.dirty or entry[0].numel() < dyn_bytes:
-            if entry is None or entry[0].numel() < dyn_bytes:
-                entry = [torch.empty(dyn_bytes, dtype=torch.uint8, device=self.device), None, 0, None]
-                self._dyn_resident[image.block_id] = entry
+            dyn = self._dyn_resident.get(image.block_id)
+            if dyn is None or dyn.buffer.numel() < dyn_bytes:
+                dyn = _DynResident(torch.empty(dyn_bytes, dtype=torch.uint8, device=self.device), Event(False))
+                self._dyn_resident[image.block_id] = dyn
                 fresh = acquire_event().record(torch.cuda.current_stream(self.device))
                 fresh.block_stream(self.copy_stream)     # memory handed out by the allocator may still be in use there
                 release_event(fresh)
-            if entry[3] is not None:
-                entry[3].block_stream(self.copy_stream)          # the last kernel that read the buffer is done
-            _native.check(self._lib.sh_copy_h2d_async(entry[0].data_ptr(), dynamic_host.buffer.data_ptr(), dyn_bytes,
-                                                      stream_handle(self.copy_stream)), "sh_copy_h2d_async")
-            release_event(dynamic_host.last_copy)
-            dynamic_host.last_copy = acquire_event().record(self.copy_stream)
-            dynamic_host.last_copy.block_stream(self.dequant_stream)
-            dynamic_host.dirty = False
-            link_bytes = dyn_bytes
-            merged = [static_descs[i] for i in range(n_static)]
-            base = entry[0].data_ptr()
+                dynamic_host.dirty = True
+            if dynamic_host.dirty:
+                if dyn.read_once:
+                    dyn.last_read.block_stream(self.copy_stream)     # the last kernel that read the buffer is done
+                _native.check(self._lib.sh_copy_h2d_async(dyn.buffer.data_ptr(), dynamic_host.buffer.data_ptr(), dyn_bytes,
+                                                          stream_handle(self.copy_stream)), "sh_copy_h2d_async")
+                if dynamic_host.last_copy is None:
+                    dynamic_host.last_copy = Event(False)
+                dynamic_host.last_copy.record(self.copy_stream)
+                dynamic_host.dirty = False
+                link_bytes, src_ready = dyn_bytes, dynamic_host.last_copy.handle
+            ready3 = dyn.last_read.handle
+            dyn.read_once = True
+
+        stamp = (id(image), image.desc_version, id(source), bool(pieces), dyn.buffer.data_ptr() if dyn else 0,
+                 bool(fused))
+        reg = self._registered.get((image.block_id, "device"))
+        if reg is None or reg.stamp != stamp:
+            rows = []
+            for i in range(n_static):
+                d = ShParamDesc()
+                ctypes.memmove(ctypes.byref(d), ctypes.byref(static_descs[i]), ctypes.sizeof(ShParamDesc))
+                if source.descs is None and fused and source.is_peer:
+                    d.flags |= _native.SH_DESC_PEER_SOURCE
+                rows.append(d)
             for i in range(n_dyn):
-                d = _native.ShParamDesc()
-                ctypes.memmove(ctypes.byref(d), ctypes.byref(dyn_descs[i]), ctypes.sizeof(_native.ShParamDesc))
+                d = ShParamDesc()
+                ctypes.memmove(ctypes.byref(d), ctypes.byref(dyn_descs[i]), ctypes.sizeof(ShParamDesc))
                 if d.kind != _native.SH_KIND_ZERO:
                     d.flags |= _native.SH_DESC_ABSOLUTE
-                    d.src_off += base
-                merged.append(d)
-            entry[1], entry[2] = _native.make_descs(merged), len(merged)
-        _native.check(self._lib.sh_dequant_block_async(
-            entry[1], entry[2], packed_ptr, static_bytes, out_slab.tensor.data_ptr(), image.out_bytes,
-            image.out_dtype_code, stream_handle(self.dequant_stream), self.status.data_ptr()),
-            f"sh_dequant_block_async({image.block_id})")
-        release_event(entry[3])
-        entry[3] = acquire_event().record(self.dequant_stream)
-        ready = acquire_event().record(self.dequant_stream)
-        return StreamTicket(image.block_id, ready, None, link_bytes=link_bytes, peer_bytes=peer_bytes,
-                            launches=-(-entry[2] // _native.MAX_DESCS_PER_LAUNCH))
+                    d.src_off += dyn.buffer.data_ptr()
+                rows.append(d)
+            merged = _native.make_descs(rows)
+            reg = self._register((image.block_id, "device"), stamp, merged, len(rows), span, image.out_bytes,
+                                 image.out_dtype_code, pieces=pieces, keepalive=(image, source, merged))
+
+        what = f"sh_block_load({image.block_id})"
+        if pieces:
+            if self.copy_stream2 is None and len(pieces) > 1:
+                self.copy_stream2 = torch.cuda.Stream(device=self.device, priority=-1)
+            staging, staging_free = self._take_staging(span)
+            copied = acquire_event()
+            self._load(reg, what, src=0, kind=_native.SH_SRC_GATHER, staging=staging.tensor.data_ptr(), out_slab=out_slab,
+                       staging_free=staging_free, src_ready=src_ready, copied=copied.handle, ready=ready.handle,
+                       ready2=staging.last_use.handle, ready3=ready3, two_copy_streams=True)
+        else:
+            copied = None
+            self._load(reg, what, src=source.ptr, kind=_native.SH_SRC_DEVICE, staging=0, out_slab=out_slab,
+                       src_ready=src_ready, ready=ready.handle, ready3=ready3)
+        return StreamTicket(image.block_id, ready, copied, link_bytes=link_bytes, peer_bytes=peer_bytes,
+                            launches=reg.launches)
 
     # ── status ───────────────────────────────────────────────────────
 
+    def poll_status(self) -> int:
+        """Sticky status bits seen so far, without waiting: queues an asynchronous read-back of the device
+        word on the dequant stream and looks at the previous one if it has landed (``sh_status_poll``)."""
+        bits = ctypes.c_int32(0)
+        _native.check(self._lib.sh_status_poll(self.status.data_ptr(), stream_handle(self.dequant_stream),
+                                               ctypes.byref(bits)), "sh_status_poll")
+        self._status_bits |= int(bits.value)
+        return self._status_bits
+
     def read_status(self) -> int:
-        """Device status word (host-synchronising; call off the steady path, e.g. at shutdown or in tests)."""
-        return int(self.status.item())
+        """Device status word plus every bit polled earlier (host-synchronising; for shutdown and tests)."""
+        return int(self.status.item()) | self.poll_status() | self._status_bits
 
     def drain(self, timeout_ms: int = 60_000) -> None:
-        for stream in (self.copy_stream, self.dequant_stream):
-            _native.check(self._lib.sh_stream_synchronize(stream_handle(stream), timeout_ms), "sh_stream_synchronize")
+        for stream in (self.copy_stream, self.copy_stream2, self.dequant_stream):
+            if stream is not None:
+                _native.check(self._lib.sh_stream_synchronize(stream_handle(stream), timeout_ms), "sh_stream_synchronize")
+
+    def close(self) -> None:
+        """Drop every registration and the status watch (after :meth:`drain`)."""
+        self.forget()
+        self._lib.sh_status_forget(self.status.data_ptr())

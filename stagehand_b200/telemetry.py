@@ -4,7 +4,11 @@
 with its meaning: ``h2d_bytes`` stays "runtime-dtype bytes that became valid in
 VRAM" (what the reference counts, ``scheduler.py:951``).  What actually crossed the
 link on the INT8 path is reported in the added ``link_bytes`` / ``peer_bytes``
-fields, and the block kernel's launches in ``dequant_launches``.  A block that was
+fields, and the block kernel's launches in ``dequant_launches``.  With
+``StagehandConfig.telemetry_block_timings`` three device-side times are filled from CUDA events that
+are only ever *queried*, never waited for: ``copy_time_ms`` (the reference declares this field and
+never fills it, ``telemetry.py:31``), ``dequant_time_ms`` and ``exposed_stall_ms``; an event that has
+not completed when a step ends is counted in the step in which it is found complete.  A block that was
 found mid-transfer but whose weights were already complete on the device counts as
 a hit (``prefetch_hits``) and, separately, as ``soft_hits``; the reference counts
 every such block as a miss because it only reaches GPU_READY inside
@@ -48,6 +52,9 @@ class StepMetrics:
     dequant_launches: int = 0    # block-kernel launches
     soft_hits: int = 0           # blocks in flight at use time that needed no host wait
     image_cache_hits: int = 0    # loads whose packed image was already in pinned memory
+    dequant_time_ms: float = 0.0     # device time of the block kernel, summed over the blocks harvested this step
+    exposed_stall_ms: float = 0.0    # device time the compute stream spent waiting for a block's ready event
+    timed_blocks: int = 0            # blocks whose kernel time is in dequant_time_ms
 
 
 class StagehandTelemetry:
@@ -101,6 +108,11 @@ class StagehandTelemetry:
 
     def record_image_cache_hit(self) -> None:
         self._bump(image_cache_hits=1)
+
+    def record_device_times(self, copy_ms: float = 0.0, dequant_ms: float = 0.0, exposed_stall_ms: float = 0.0,
+                            timed_blocks: int = 0) -> None:
+        self._bump(copy_time_ms=copy_ms, dequant_time_ms=dequant_ms, exposed_stall_ms=exposed_stall_ms,
+                   timed_blocks=timed_blocks)
 
     def record_stall(self, duration_ms: float) -> None:
         self._bump(stall_time_ms=duration_ms, stall_count=1)
@@ -163,7 +175,9 @@ class StagehandTelemetry:
         total = m.host_pool_free + m.host_pool_in_use
         return (f"[STAGEHAND step={m.step}] hit={self.hit_rate() * 100.0:.1f}% stall={m.stall_time_ms:.1f}ms "
                 f"evict={m.evictions} vram={m.vram_used_mb / 1024.0:.1f}G pool={m.host_pool_free}/{total} "
-                f"link={m.link_bytes / 1e6:.0f}MB dq={m.dequant_launches}")
+                f"link={m.link_bytes / 1e6:.0f}MB dq={m.dequant_launches}"
+                + (f" copy={m.copy_time_ms:.1f}ms link={m.link_bytes / m.copy_time_ms / 1e6:.1f}GB/s "
+                   f"dq={m.dequant_time_ms:.1f}ms exposed={m.exposed_stall_ms:.1f}ms" if m.copy_time_ms > 0 else ""))
 
     def close(self) -> None:
         if self._file_handle is not None:

@@ -224,8 +224,10 @@ def test_bad_descriptors_are_rejected_before_launch() -> None:
 
 @pytest.mark.parametrize("rows,cols", [(12288, 49152), (21504, 3072)])
 def test_full_size_matrices_through_size_independent_properties(rows: int, cols: int) -> None:
-    """The largest sweep shapes, where the CPU oracle would take minutes: properties that need no oracle.
+    """The largest sweep shapes: the scalar-C oracle on the smaller of the two (seconds), and for both the
+    properties that need no oracle.
 
+    * 21504 x 3072: every output byte equals the C oracle's (``sq_ref_dequant_rows_fast``);
     * an independent GPU formulation (torch ops: int8 -> fp32, multiply, cast) gives the same bytes;
     * negating the weights negates every output exactly;
     * doubling every scale doubles every output exactly (a power-of-two factor commutes with rounding);
@@ -257,6 +259,12 @@ def test_full_size_matrices_through_size_independent_properties(rows: int, cols:
     base = run(q, scale)
     again = run(q, scale)
     assert torch.equal(base.view(torch.int16), again.view(torch.int16))
+    if n <= 21504 * 3072:
+        from oracle import c_oracle
+
+        ref_bytes = c_oracle.dequant_rows(q.view(rows, cols).cpu().numpy(), cols, scale.cpu().numpy(), None, rows, cols,
+                                          "bf16", fast=True)
+        assert np.array_equal(base.view(torch.int16).cpu().numpy().view(np.uint8).reshape(-1), ref_bytes)
     chunk = 1024
     for r0 in range(0, rows, chunk):                               # independent formulation, chunked to bound memory
         ref = (q.view(rows, cols)[r0 : r0 + chunk].float() * scale[r0 : r0 + chunk, None]).to(torch.bfloat16)

@@ -111,6 +111,33 @@ def test_eviction_and_reload_under_a_tight_budget(cache_mb: int, tmp_path: Path)
     assert rt._pool.stats()["in_use"] == 0 if cache_mb else True
 
 
+def test_per_block_device_timings_reach_the_step_metrics(tmp_path: Path) -> None:
+    """copy / dequant / exposed-stall times come from CUDA events that are polled, never waited for."""
+    import time
+
+    model, rt, x = _build("cfg1", tmp_path, telemetry_block_timings=True, nvtx_ranges=True,
+                          vram_high_watermark_mb=70, vram_low_watermark_mb=40)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    rt.begin_step(0)
+    with torch.inference_mode(), rt.managed_forward():
+        model(x)
+    torch.cuda.synchronize()                      # so that every event of the step has completed when it is polled
+    rt.end_step()
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    m = rt.telemetry.last()
+    assert m.timed_blocks == 4 and m.dequant_launches == 4
+    assert m.copy_time_ms > 0 and m.dequant_time_ms > 0 and m.exposed_stall_ms > 0
+    assert m.copy_time_ms + m.dequant_time_ms + m.exposed_stall_ms < wall_ms
+    # 12.6 MB per block over the host link: between 2 and 80 GB/s whatever the box
+    gbs = m.link_bytes / m.copy_time_ms / 1e6
+    assert 2.0 < gbs < 80.0, gbs
+    rt.shutdown()
+    from stagehand_b200 import _native
+
+    _native.check(_native.lib().sh_profile_enable(0))
+
+
 def test_resident_blocks_are_hits_on_later_steps(tmp_path: Path) -> None:
     model, rt, x = _build("small", tmp_path)
     for step in range(3):
@@ -123,18 +150,20 @@ def test_resident_blocks_are_hits_on_later_steps(tmp_path: Path) -> None:
     rt.shutdown()
 
 
-@pytest.mark.parametrize("layout,fused,world", [("owner", True, 3), ("owner", False, 3), ("striped", True, 3),
-                                               ("striped", True, 8)])
-def test_sharded_layouts_emulated_on_one_gpu(layout: str, fused: bool, world: int, tmp_path: Path) -> None:
+@pytest.mark.parametrize("layout,fused,world,gather", [("owner", True, 3, False), ("owner", False, 3, False),
+                                                      ("striped", True, 3, False), ("striped", True, 8, False),
+                                                      ("striped", True, 2, True), ("striped", True, 8, True)])
+def test_sharded_layouts_emulated_on_one_gpu(layout: str, fused: bool, world: int, gather: bool, tmp_path: Path) -> None:
     """One process plays every rank: arenas for all ranks on this GPU, peers read through the plain-load path.
 
     Bit-exact block images and the forward within tolerance, for the owner layout (fused and copy-engine
-    staged) and for the row-striped layout (absolute-address descriptors).
+    staged) and for the row-striped layout (absolute-address descriptors read in place, or one copy-engine
+    pull per owner into the staging slab and offset descriptors).
     """
     from stagehand_b200.sharded import DeviceImageStore
 
     model, rt, x = _build("cfg1", tmp_path)
-    store = DeviceImageStore(rt, layout=layout, fused=fused, emulate_world=world)
+    store = DeviceImageStore(rt, layout=layout, fused=fused, emulate_world=world, gather=gather)
     rt.begin_step(0)
     with torch.inference_mode(), rt.managed_forward():
         y = model(x)
@@ -153,6 +182,16 @@ def test_sharded_layouts_emulated_on_one_gpu(layout: str, fused: bool, world: in
     else:
         assert abs(m.peer_bytes - total_int8 * (world - 1) / world) < 0.05 * total_int8
     assert m.link_bytes < 4 * 20_000
+    rt.end_step()
+    # a second pass re-loads evicted blocks through the registered plans (and the reused staging slabs)
+    rt.begin_step(1)
+    with torch.inference_mode(), rt.managed_forward():
+        y2 = model(x)
+    torch.cuda.synchronize()
+    assert torch.equal(y, y2) and rt._scheduler._streamer.read_status() == 0
+    if gather:
+        from stagehand_b200 import _native
+        assert _native.stats()["peer_copies"] >= (world - 1) * 4
     rt.end_step()
     rt.shutdown()
     store.close()

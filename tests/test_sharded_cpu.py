@@ -146,6 +146,29 @@ def test_stripes_cover_every_row_once_and_rebuild_the_block() -> None:
             assert d.src_off % 16 == 0 and d.scale_off % 16 == 0
         assert np.all(covered == 1)                             # every output byte produced exactly once
         assert np.array_equal(out, expected)
+        # copy-engine gather: a consumer pulls every other rank's chunk of the block into one staging buffer
+        # (one copy per owner) and expands remote stripes from there, its own stripes from its arena
+        from stagehand_b200.sharded import plan_gather
+
+        for consumer in {0, world - 1}:
+            staged_at, staging_bytes, copies = plan_gather(stripes.chunks, consumer, world)
+            assert [c[0] for c in copies] == [r for r in ((consumer + k) % world for k in range(1, world))
+                                              if r in stripes.chunks]
+            staging = np.full(staging_bytes + 64, 0xAB, dtype=np.uint8)
+            for owner, at, staged, nbytes in copies:
+                assert at % 4096 == 0 and staged % 4096 == 0
+                staging[staged : staged + nbytes] = arenas[owner][at : at + nbytes]
+            out2 = np.full(dst, 0xEE, dtype=np.uint8)
+            for d in stripes.descs:
+                local = d.rank == consumer or d.kind == _native.SH_KIND_ZERO
+                shift = 0 if local else staged_at[d.rank] - stripes.chunks[d.rank][0]
+                one = ShParamDesc(kind=d.kind, flags=0, src_off=d.src_off + shift, scale_off=d.scale_off + shift,
+                                  zp_off=d.zp_off + shift if d.zp_off >= 0 else -1, dst_off=d.dst_off, rows=d.rows,
+                                  cols=d.cols, ld=d.ld)
+                part = expand(arenas[d.rank] if local else staging, [one], 1, dst, _native.SH_DT_BF16)
+                nbytes = d.rows * d.cols * 2 if d.kind in (_native.SH_KIND_DEQUANT_I8, _native.SH_KIND_CAST_F32) else d.cols
+                out2[d.dst_off : d.dst_off + nbytes] = part[d.dst_off : d.dst_off + nbytes]
+            assert np.array_equal(out2, expected)
         if world == 8:                                          # the load is spread: no rank holds most of the bytes
             per_rank = [sum(p.nbytes for p in stripes.pieces if p.rank == r) for r in range(world)]
             assert max(per_rank) < 0.4 * sum(per_rank)

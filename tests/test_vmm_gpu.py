@@ -130,3 +130,74 @@ def test_background_prefetch_overlaps_the_caller(alloc: SlabAllocator) -> None:
     alloc.wait_prefetch(1000)
     with pytest.raises(ValueError):
         alloc.prefetch(slab, 999)
+
+
+def _keep_stream_busy(stream: torch.cuda.Stream, ms: float = 150.0) -> torch.cuda.Event:
+    """Queue ordinary work (matrix products) on *stream* for roughly *ms*; returns the event recorded after it."""
+    a = torch.randn(4096, 4096, device="cuda", dtype=torch.bfloat16)
+    with torch.cuda.stream(stream):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(20):
+            a @ a
+        e1.record()
+    e1.synchronize()
+    per_product = max(e0.elapsed_time(e1) / 20, 1e-3)
+    done = torch.cuda.Event()
+    with torch.cuda.stream(stream):
+        for _ in range(int(ms / per_product) + 1):
+            a @ a
+        done.record()
+    return done
+
+
+def test_a_busy_released_region_is_passed_over_for_an_idle_one(alloc: SlabAllocator) -> None:
+    """Region A was released behind work that is still running, region B is idle: making room for C takes B,
+    at once, although A is the least recently used (a release event that has not completed keeps a region)."""
+    import time
+
+    g = alloc.stats()["granularity"]
+    alloc.set_vram_ceiling(2 * g)
+    slab = alloc.create_slab(3 * g)
+    a, b, c = (alloc.define_region(slab, i * g, g) for i in range(3))
+    busy = torch.cuda.Stream()
+    ha = alloc.ensure_resident(slab, a)
+    hb = alloc.ensure_resident(slab, b)
+    hb.release(torch.cuda.current_stream().cuda_stream)      # idle stream: complete at once
+    torch.cuda.synchronize()
+    done = _keep_stream_busy(busy)
+    ha.release(busy.cuda_stream)                              # A's release sits behind ~150 ms of queued work
+    before = alloc.stats()["evictions"]
+    t0 = time.monotonic()
+    hc = alloc.ensure_resident(slab, c)
+    waited_ms = (time.monotonic() - t0) * 1e3
+    still_running = not done.query()
+    assert alloc.stats()["evictions"] == before + 1
+    # A is still mapped: holding it again costs no map, and no further eviction
+    ha2 = alloc.ensure_resident(slab, a)
+    assert alloc.stats()["evictions"] == before + 1 and alloc.stats()["mapped_regions"] == 2
+    assert still_running, "the queued work finished before the request was made; nothing was tested"
+    assert waited_ms < 50.0, f"mapping C took {waited_ms:.1f} ms: it waited for A's stream"
+    done.synchronize()
+    for h in (hc, ha2):
+        h.release()
+    alloc.destroy_slab(slab)
+
+
+def test_two_holders_releasing_on_two_streams_are_both_honoured(alloc: SlabAllocator) -> None:
+    """The second release (idle stream) must not hide the first one's stream: the region stays until both are done."""
+    g = alloc.stats()["granularity"]
+    alloc.set_vram_ceiling(g)
+    slab = alloc.create_slab(2 * g)
+    a, b = alloc.define_region(slab, 0, g), alloc.define_region(slab, g, g)
+    busy = torch.cuda.Stream()
+    h1 = alloc.ensure_resident(slab, a)
+    h2 = alloc.ensure_resident(slab, a)
+    done = _keep_stream_busy(busy)
+    h1.release(busy.cuda_stream)
+    h2.release(torch.cuda.current_stream().cuda_stream)
+    hb = alloc.ensure_resident(slab, b)                       # has to wait (bounded) for the busy stream, then evicts A
+    assert done.query(), "A was unmapped while the first holder's stream still had work queued"
+    assert alloc.stats()["mapped_regions"] == 1
+    hb.release()
+    alloc.destroy_slab(slab)

@@ -5,9 +5,12 @@ server that gave the whole GPU to its own allocator at start-up, a plug-in that 
 initialisation, a loop where an allocation would stall the device.  For them the library carries a
 fixed staging array of its own (``SH_NOALLOC_MAX_BYTES`` per GPU).  This test drives that entry point
 through the C ABI twice in a row, with two different images, and requires the output bytes to equal
-what the ordinary entry point produces for the same images (bit-exact: the tolerance every other
-kernel test here uses).  The file sorts last so a run that stops at the first failure has already
-run every other test.
+what the ordinary entry point produces for the same images AND what the CPU oracle computes from the
+same bytes (bit-exact: the tolerance every other kernel test here uses).  It also watches the
+driver's own count of free device memory (``cudaMemGetInfo``) across the two calls: after
+``sh_init`` and one warm-up call have paid for the library's device image, the entry point must not
+take a byte more.  The file sorts last so a run that stops at the first failure has already run
+every other test.
 """
 from __future__ import annotations
 
@@ -15,6 +18,7 @@ import numpy as np
 import pytest
 import torch
 
+from desc_interp import expand
 from kernel_utils import DT_CODE, HandImage, align
 from stagehand_b200 import _native
 
@@ -34,12 +38,17 @@ def _image(seed: int) -> HandImage:
     return img
 
 
-def _run(img: HandImage, no_alloc: bool) -> np.ndarray:
-    lib = _native.lib()
-    _native.check(lib.sh_init(torch.cuda.current_device()), "sh_init")
+def _buffers(img: HandImage):
     host = torch.from_numpy(img.host_bytes()).pin_memory()
     out = torch.full((align(img.dst_cursor, 256),), 0xEE, dtype=torch.uint8, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    return host, out, status
+
+
+def _run(img: HandImage, no_alloc: bool, buffers=None) -> np.ndarray:
+    lib = _native.lib()
+    _native.check(lib.sh_init(torch.cuda.current_device()), "sh_init")
+    host, out, status = buffers if buffers is not None else _buffers(img)
     descs = _native.make_descs(img.descs)
     stream = torch.cuda.current_stream().cuda_stream
     torch.cuda.synchronize()
@@ -61,13 +70,24 @@ def _run(img: HandImage, no_alloc: bool) -> np.ndarray:
 def test_no_alloc_entry_point_matches_the_streaming_entry_point_twice_in_a_row() -> None:
     first, second = _image(101), _image(202)
     expect_first, expect_second = _run(first, no_alloc=False), _run(second, no_alloc=False)
+    _run(_image(303), no_alloc=True)             # warm-up: the library's device image is on the GPU from here on
+    # every buffer the two calls need exists before the count of free memory is taken
+    buffers_first, buffers_second = _buffers(first), _buffers(second)
+    torch.cuda.synchronize()
     before = torch.cuda.memory_allocated()
-    got_first = _run(first, no_alloc=True)
-    got_second = _run(second, no_alloc=True)     # the shared staging array still holds the first image
+    free_before = torch.cuda.mem_get_info()[0]   # cudaMemGetInfo: sees any allocation, whoever made it
+    got_first = _run(first, no_alloc=True, buffers=buffers_first)
+    got_second = _run(second, no_alloc=True, buffers=buffers_second)     # the shared array still holds the first image
+    free_after = torch.cuda.mem_get_info()[0]
     assert np.array_equal(got_first, expect_first)
     assert np.array_equal(got_second, expect_second)
     assert not np.array_equal(got_first, got_second)
     assert torch.cuda.memory_allocated() == before
+    assert free_after >= free_before, f"{free_before - free_after} bytes of device memory were taken during the calls"
+    # and against the CPU oracle, so that the comparison does not rest on another CUDA path alone
+    for img, got in ((first, got_first), (second, got_second)):
+        ref = expand(img.host_bytes(), img.descs, len(img.descs), got.size, DT_CODE["bf16"])
+        assert np.array_equal(got, ref)
 
 
 def test_no_alloc_entry_point_rejects_images_beyond_its_staging_area() -> None:

@@ -73,3 +73,29 @@ def cast_f32(src: np.ndarray, runtime_dtype: str = "bf16") -> np.ndarray:
     out = np.empty(src.size * _ITEMSIZE[runtime_dtype], dtype=np.uint8)
     lib.sq_ref_cast_f32(src.ctypes.data, src.size, out.ctypes.data, OUT_CODES[runtime_dtype])
     return out
+
+
+def dequant_rows_threaded(qweight: np.ndarray, scale: np.ndarray, zero_point: np.ndarray | None, out_features: int,
+                          in_features: int, runtime_dtype: str = "bf16", threads: int = 0) -> np.ndarray:
+    """Same call as ``squareq_oracle.dequant_rows``, computed by ``sq_ref_dequant_rows_fast`` on row ranges
+    handed to *threads* host threads (default: every core this process may use).  Returns bytes."""
+    import os
+    from concurrent.futures import ThreadPoolExecutor
+
+    lib = load()
+    q = np.ascontiguousarray(qweight.reshape(qweight.shape[0], -1), dtype=np.int8)
+    ld = int(q.shape[1])
+    s = np.ascontiguousarray(np.asarray(scale).reshape(-1)[:out_features], dtype=np.float32)
+    z = None if zero_point is None else np.ascontiguousarray(np.asarray(zero_point).reshape(-1)[:out_features], dtype=np.float32)
+    out = np.empty(out_features * in_features * _ITEMSIZE[runtime_dtype], dtype=np.uint8)
+    n = threads or (len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
+    n = max(1, min(n, out_features))
+    bounds = [out_features * i // n for i in range(n + 1)]
+
+    def work(i: int) -> None:
+        lib.sq_ref_dequant_rows_fast(q.ctypes.data, ld, s.ctypes.data, None if z is None else z.ctypes.data,
+                                     bounds[i], bounds[i + 1], in_features, out.ctypes.data, OUT_CODES[runtime_dtype])
+
+    with ThreadPoolExecutor(max_workers=n) as pool:
+        list(pool.map(work, range(n)))
+    return out

@@ -173,6 +173,7 @@ def stage_block(
     squareq_layers: Mapping[str, Mapping[str, object]],
     module_params: Mapping[str, tuple[np.ndarray, str]],
     module_param_cache: MutableMapping[str, tuple[np.ndarray, str]] | None = None,
+    dequant=None,
 ) -> None:
     """Fill the uint8 *buffer* with one block's runtime-dtype image.
 
@@ -187,8 +188,10 @@ def stage_block(
     whose element count differs from the layout row stands for a parameter that
     eviction emptied, in which case the cache is consulted
     (``scheduler.py:318-322``).  Whatever cannot be resolved is zero-filled
-    (``scheduler.py:325``).
+    (``scheduler.py:325``).  *dequant* replaces :func:`dequant_rows` (same signature) -- the
+    scalar-C restatement split over host threads, for blocks of hundreds of millions of weights.
     """
+    dequant = dequant or dequant_rows
     for name, shape, dtype, offset, numel in layout:
         nbytes = numel * RUNTIME_DTYPES[dtype]
         region = buffer[offset : offset + nbytes]
@@ -214,7 +217,7 @@ def stage_block(
                         if s.reshape(-1)[:out_dim].size != out_dim or z.reshape(-1)[:out_dim].size != out_dim:
                             region[:] = 0
                             continue
-                        region[:] = dequant_rows(q, s, z, out_dim, in_flat, dtype)
+                        region[:] = dequant(q, s, z, out_dim, in_flat, dtype)
                         continue
                     # a layer dict with a missing tensor falls through to the module path
                 elif kind == "bias":

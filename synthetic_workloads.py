@@ -251,6 +251,7 @@ class MistralShapedEncoder(nn.Module):
     def __init__(self, n_layers: int = 40, hidden: int = 5120, q_heads: int = 32, kv_heads: int = 8,
                  head_dim: int = 128, ffn: int = 32768, device=None, dtype=None) -> None:
         super().__init__()
+        self.hidden = hidden
         self.layers = nn.ModuleList(
             _GqaLayer(hidden, q_heads, kv_heads, head_dim, ffn, device, dtype) for _ in range(n_layers))
 
@@ -471,14 +472,18 @@ def synth_squareq_layer(out_features: int, in_features: int, generator: torch.Ge
 
 def write_squareq_fpk(model: nn.Module, block_pattern: str, path: str | Path, seed: int = 0,
                       share_storage: bool = False, pad_in_to: int | None = None,
-                      scale_median: float = 0.01) -> dict[str, int]:
+                      scale_median: float = 0.01, distinct_scales: bool = False) -> dict[str, int]:
     """Write a SquareQ BP8 ``.fpk`` covering every ``nn.Linear`` inside the matched blocks.
 
     Layer names are ``"<block_id>.<linear path>"``.  With *share_storage* every
     layer of one ``(out, in)`` shape reuses a single set of tensors, so the file
     holds one copy per distinct shape (``torch.save`` writes a shared storage
     once) while the runtime still stages every block separately; this keeps the
-    set-up of multi-gigabyte configurations short.  With *pad_in_to* the stored
+    set-up of multi-gigabyte configurations short.  With *distinct_scales* a layer that
+    shares its tensors still gets a scale vector of its own (the shared one times a
+    layer-specific factor in [1, 1.06)): the file stays small, yet no two blocks expand to
+    the same bytes, so a digest of a delivered block also proves that it was built from
+    *its* rows and scales.  With *pad_in_to* the stored
     rows are padded to a multiple of that many columns (``padded_in > in``).
 
     Returns ``{"layers": n, "elements": total int8 weights}``.
@@ -507,6 +512,8 @@ def write_squareq_fpk(model: nn.Module, block_pattern: str, path: str | Path, se
                 by_shape[key] = layer
             name = f"{block_id}.{sub_name}" if sub_name else block_id
             layers[name] = dict(layer)
+            if distinct_scales and share_storage:
+                layers[name]["scale"] = layer["scale"] * (1.0 + (len(manifest_layers) % 61) / 1024.0)
             manifest_layers.append(
                 {"name": name, "out": out_f, "inp": in_f, "padded_in": padded, "has_bias": has_bias})
             elements += out_f * in_f

@@ -121,5 +121,12 @@ def test_stage_block_matches_reference() -> None:
     buf = np.full(total, 0xCD, dtype=np.uint8)
     oracle.stage_block(buf, layout, specs, {str(n) for n in g["module_names"]}, layers, live, cache)
     assert np.array_equal(buf, g["ref"])
+    # the same block with the threaded scalar-C dequant plugged in (what the benchmark's parity leg uses)
+    from oracle import c_oracle
+
+    buf2 = np.full(total, 0xCD, dtype=np.uint8)
+    oracle.stage_block(buf2, layout, specs, {str(n) for n in g["module_names"]}, layers, dict(live), dict(cache),
+                       dequant=lambda *a: c_oracle.dequant_rows_threaded(*a, threads=3))
+    assert np.array_equal(buf2, g["ref"])
     # the cache gained the module-owned parameters that were staged from live data
     assert sorted(cache) == [str(n) for n in g["cache_after"]]

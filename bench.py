@@ -97,6 +97,8 @@ def parse_args() -> argparse.Namespace:
                     help="video_train: load backward-pass blocks on demand, as the reference does")
     ap.add_argument("--peer-ctas-per-sm", type=int, default=0,
                     help="multi-GPU: CTAs per SM a block-kernel launch that reads peer memory may occupy (0 = no cap)")
+    ap.add_argument("--peer-deep-loads", action="store_true",
+                    help="multi-GPU, fused delivery: the block-kernel variant with 8 loads in flight per thread, 4 CTAs per SM")
     ap.add_argument("--dequant-priority", type=int, default=-1, help="CUDA priority of the block kernel's stream")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--skip-delivery-only", action="store_true")
@@ -1118,7 +1120,7 @@ def main() -> None:
                 store = DeviceImageStore(rt, rank=rank, world=world, fused=not args.no_fused,
                                          layout=args.layout if world > 1 else "owner",
                                          peer_ctas_per_sm=args.peer_ctas_per_sm,
-                                         gather=args.delivery == "gather")
+                                         gather=args.delivery == "gather", peer_deep_loads=args.peer_deep_loads)
             device_inputs = [t.cuda() for t in host_inputs]
             host_io = name == "e2e"
             step = [0]

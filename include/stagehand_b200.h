@@ -172,6 +172,14 @@ int32_t sh_device_free(void* ptr);
 int32_t sh_pack_rows(void* dst, int64_t dst_ld, const void* src, int64_t src_ld,
                      int64_t rows, int64_t row_bytes, int32_t n_threads);
 
+/*
+ * Host memory: make dst[0, bytes) equal src[0, bytes), writing only when they differ; *changed_out says
+ * whether they did.  Keeps the small module-owned parameters (norm weights, biases) of a packed image
+ * current without touching it when nothing changed -- the reference restages them at every load
+ * (src/stagehand/scheduler.py:310-322).
+ */
+int32_t sh_sync_bytes(void* dst, const void* src, size_t bytes, int32_t* changed_out);
+
 /* ── data movement ───────────────────────────────────────────────────── */
 
 /*
@@ -362,6 +370,15 @@ int32_t sh_vram_pool_destroy(uint64_t pool);
  * reference, which has no multi-GPU path.  Negative values are treated as 0.
  */
 int32_t sh_set_peer_ctas_per_sm(int32_t ctas_per_sm);
+
+/*
+ * Variant of the block kernel for blocks that read another GPU's memory: 8 instead of 4 sixteen-byte loads in
+ * flight per thread and at most 4 instead of 16 CTAs resident per SM, so the NVLink latency is covered by
+ * bytes in flight per thread rather than by the number of waiting threads.  Applies to plans built (or blocks
+ * registered) after the call; off by default; results are identical either way.  No counterpart in the
+ * reference.
+ */
+int32_t sh_set_peer_deep_loads(int32_t on);
 
 /*
  * Per-launch device timing of the block kernel (CUDA events on the launching

@@ -119,6 +119,7 @@ _SIGNATURES: dict[str, list] = {
     "sh_device_alloc": [c_size_t, POINTER(c_void_p)],
     "sh_device_free": [c_void_p],
     "sh_pack_rows": [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int32],
+    "sh_sync_bytes": [c_void_p, c_void_p, c_size_t, POINTER(c_int32)],
     "sh_copy_h2d_async": [c_void_p, c_void_p, c_size_t, c_uint64],
     "sh_pull_block_async": [c_void_p, c_void_p, c_size_t, c_uint64],
     "sh_peer_enable": [c_int32],
@@ -174,6 +175,7 @@ _SIGNATURES: dict[str, list] = {
     "sh_vram_pool_stats": [c_uint64, POINTER(ShPoolStats)],
     "sh_vram_pool_destroy": [c_uint64],
     "sh_set_peer_ctas_per_sm": [c_int32],
+    "sh_set_peer_deep_loads": [c_int32],
     "sh_profile_enable": [c_int32],
     "sh_profile_collect": [POINTER(c_double), POINTER(c_int64), POINTER(c_int64), POINTER(c_int64), c_int32],
     "sh_profile_poll": [POINTER(ShProfileSums)],

@@ -42,6 +42,7 @@ class BudgetManager:
         # for a short time.  invalidate() drops it (the device pool calls it when it really allocates).
         self._reading_ttl_s = 0.0005
         self._reading: tuple[float, int] | None = None
+        self._cuda: bool | None = None
 
     def set_reusable_bytes_source(self, fn: Callable[[], int] | None) -> None:
         """Register a callable returning allocator-visible bytes that are free for reuse."""
@@ -55,8 +56,15 @@ class BudgetManager:
         """Forget the cached allocator reading (call after a large allocation or free)."""
         self._reading = None
 
+    def _has_cuda(self) -> bool:
+        # asked several times per block; torch's own check goes through the environment and NVML every time
+        hit = self._cuda
+        if hit is None:
+            hit = self._cuda = bool(torch.cuda.is_available())
+        return hit
+
     def vram_used_mb(self) -> float:
-        if not torch.cuda.is_available():
+        if not self._has_cuda():
             return 0.0
         now = time.monotonic()
         if self._reading is None or now - self._reading[0] > self._reading_ttl_s:
@@ -69,7 +77,7 @@ class BudgetManager:
         return used / _MB
 
     def vram_reserved_mb(self) -> float:
-        if not torch.cuda.is_available():
+        if not self._has_cuda():
             return 0.0
         return torch.cuda.memory_reserved() / _MB
 

@@ -385,6 +385,14 @@ int32_t sh_pack_rows(void* dst, int64_t dst_ld, const void* src, int64_t src_ld,
     return SH_OK;
 }
 
+int32_t sh_sync_bytes(void* dst, const void* src, size_t bytes, int32_t* changed_out) {
+    if (bytes != 0 && (dst == nullptr || src == nullptr)) return fail(SH_ERR_INVALID_ARG, "null sync pointer");
+    const bool differs = bytes != 0 && memcmp(dst, src, bytes) != 0;
+    if (differs) memcpy(dst, src, bytes);
+    if (changed_out != nullptr) *changed_out = differs ? 1 : 0;
+    return SH_OK;
+}
+
 // ── data movement ───────────────────────────────────────────────────────
 
 int32_t sh_copy_h2d_async(void* dst_dev, const void* src_host, size_t bytes, uint64_t stream) {
@@ -532,6 +540,11 @@ int32_t sh_status_forget(int32_t* status_dev) {
 
 int32_t sh_set_peer_ctas_per_sm(int32_t ctas_per_sm) {
     sq::set_peer_ctas_per_sm(ctas_per_sm);
+    return SH_OK;
+}
+
+int32_t sh_set_peer_deep_loads(int32_t on) {
+    sq::set_peer_deep_loads(on != 0);
     return SH_OK;
 }
 

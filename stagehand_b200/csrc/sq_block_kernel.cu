@@ -201,9 +201,10 @@ __device__ __forceinline__ uint32_t tile_row_of(uint32_t t, uint32_t spr, uint64
     return t >= spr ? 1u : 0u;
 }
 
-template <typename OutT, bool HasZp, bool Dense>
+template <typename OutT, bool HasZp, bool Dense, int kSegsPerThread>
 __device__ __forceinline__ void dequant_vec_tile(const DescDev& D, int64_t local_tile, float* s_scale, float* s_zp,
                                                  uint64_t* s_bar, int32_t* status, bool may_stage) {
+    constexpr int kTileSegs = kThreads * kSegsPerThread;       // shadows the namespace constants: this variant's tile
     const uint32_t spr = static_cast<uint32_t>(D.segs_per_row);
     const uint64_t magic = D.row_magic;
     const int64_t total_segs = D.rows * static_cast<int64_t>(spr);
@@ -262,7 +263,8 @@ __device__ __forceinline__ void dequant_vec_tile(const DescDev& D, int64_t local
     const uint32_t n_stage = (lead + rows_in_tile + 3u) & ~3u;
     // Staging pays when a tile spans many scale rows (short rows); with long rows a tile needs a
     // handful of scales and plain cached loads are cheaper than a barrier round trip.
-    bool staged = may_stage && (D.flags & kFlagBulkScales) != 0 && rows_in_tile >= kStageMinRows && n_stage <= kSmemRows;
+    bool staged = may_stage && (D.flags & kFlagBulkScales) != 0 && rows_in_tile >= kStageMinRows &&
+                  n_stage <= static_cast<uint32_t>(kSmemRows);
     if (staged) {
         if (threadIdx.x == 0) {
             mbar_init(s_bar, 1);
@@ -374,8 +376,8 @@ __device__ __forceinline__ void copy_zero_tile(const DescDev& D, int64_t local_t
 
 // ── the kernel ───────────────────────────────────────────────────────────
 
-template <typename OutT, bool GridStride>
-__global__ void __launch_bounds__(kThreads, GridStride ? 4 : SQ_MIN_CTAS_PER_SM)
+template <typename OutT, bool GridStride, int Segs>
+__global__ void __launch_bounds__(kThreads, (GridStride || Segs != kSegsPerThread) ? kDeepMinCtasPerSm : SQ_MIN_CTAS_PER_SM)
 sq_block_kernel(const __grid_constant__ BlockPlan plan, int32_t* status) {
     __shared__ alignas(16) float s_scale[kSmemRows];
     __shared__ alignas(16) float s_zp[kSmemRows];
@@ -402,11 +404,11 @@ sq_block_kernel(const __grid_constant__ BlockPlan plan, int32_t* status) {
     switch (D.path) {
         case kPathDequantVec:
             if (D.flags & kFlagDense) {
-                if (D.zp != nullptr) dequant_vec_tile<OutT, true, true>(D, local_tile, s_scale, s_zp, &s_bar, status, single);
-                else                 dequant_vec_tile<OutT, false, true>(D, local_tile, s_scale, s_zp, &s_bar, status, single);
+                if (D.zp != nullptr) dequant_vec_tile<OutT, true, true, Segs>(D, local_tile, s_scale, s_zp, &s_bar, status, single);
+                else                 dequant_vec_tile<OutT, false, true, Segs>(D, local_tile, s_scale, s_zp, &s_bar, status, single);
             } else {
-                if (D.zp != nullptr) dequant_vec_tile<OutT, true, false>(D, local_tile, s_scale, s_zp, &s_bar, status, single);
-                else                 dequant_vec_tile<OutT, false, false>(D, local_tile, s_scale, s_zp, &s_bar, status, single);
+                if (D.zp != nullptr) dequant_vec_tile<OutT, true, false, Segs>(D, local_tile, s_scale, s_zp, &s_bar, status, single);
+                else                 dequant_vec_tile<OutT, false, false, Segs>(D, local_tile, s_scale, s_zp, &s_bar, status, single);
             }
             break;
         case kPathDequantScalar: dequant_scalar_tile<OutT>(D, local_tile); break;
@@ -428,6 +430,10 @@ sq_block_kernel(const __grid_constant__ BlockPlan plan, int32_t* status) {
 // of every SM for that time and the model's own kernels queue behind it.
 static std::atomic<int> g_peer_ctas_per_sm{0};
 static std::atomic<int> g_sm_count{0};
+static std::atomic<bool> g_peer_deep{false};
+
+void set_peer_deep_loads(bool on) { g_peer_deep.store(on); }
+bool peer_deep_loads() { return g_peer_deep.load(); }
 
 void set_peer_ctas_per_sm(int n) { g_peer_ctas_per_sm.store(n < 0 ? 0 : n); }
 int peer_ctas_per_sm() { return g_peer_ctas_per_sm.load(); }
@@ -451,23 +457,23 @@ cudaError_t launch_plan(const BlockPlan& plan, int out_dtype, cudaStream_t strea
         const unsigned limit = static_cast<unsigned>(cap) * static_cast<unsigned>(sm_count());
         if (ctas > limit) ctas = limit;
     }
-    const dim3 grid(ctas);
-    if (ctas < static_cast<unsigned>(plan.total_tiles)) {
-        switch (out_dtype) {
-            case SH_DT_BF16: sq_block_kernel<__nv_bfloat16, true><<<grid, dim3(kThreads), 0, stream>>>(plan, status_dev); break;
-            case SH_DT_F16:  sq_block_kernel<__half, true><<<grid, dim3(kThreads), 0, stream>>>(plan, status_dev); break;
-            case SH_DT_F32:  sq_block_kernel<float, true><<<grid, dim3(kThreads), 0, stream>>>(plan, status_dev); break;
-            default: return cudaErrorInvalidValue;
-        }
-        return cudaGetLastError();
-    }
-    const dim3 block(kThreads);
+    const dim3 grid(ctas), block(kThreads);
+    const bool stride = ctas < static_cast<unsigned>(plan.total_tiles);
+    const bool deep = plan.segs_per_thread == static_cast<uint32_t>(kDeepSegsPerThread);
+#define SQ_LAUNCH(T)                                                                                              \
+    do {                                                                                                          \
+        if (deep && stride)  sq_block_kernel<T, true, kDeepSegsPerThread><<<grid, block, 0, stream>>>(plan, status_dev);   \
+        else if (deep)       sq_block_kernel<T, false, kDeepSegsPerThread><<<grid, block, 0, stream>>>(plan, status_dev);  \
+        else if (stride)     sq_block_kernel<T, true, kSegsPerThread><<<grid, block, 0, stream>>>(plan, status_dev);       \
+        else                 sq_block_kernel<T, false, kSegsPerThread><<<grid, block, 0, stream>>>(plan, status_dev);      \
+    } while (0)
     switch (out_dtype) {
-        case SH_DT_BF16: sq_block_kernel<__nv_bfloat16, false><<<grid, block, 0, stream>>>(plan, status_dev); break;
-        case SH_DT_F16:  sq_block_kernel<__half, false><<<grid, block, 0, stream>>>(plan, status_dev); break;
-        case SH_DT_F32:  sq_block_kernel<float, false><<<grid, block, 0, stream>>>(plan, status_dev); break;
+        case SH_DT_BF16: SQ_LAUNCH(__nv_bfloat16); break;
+        case SH_DT_F16:  SQ_LAUNCH(__half); break;
+        case SH_DT_F32:  SQ_LAUNCH(float); break;
         default: return cudaErrorInvalidValue;
     }
+#undef SQ_LAUNCH
     return cudaGetLastError();
 }
 
@@ -531,6 +537,11 @@ int build_plans(const ShParamDesc* descs, int n, const void* packed, size_t pack
     int n_plans = 0;
     BlockPlan* plan = nullptr;
     uint32_t tiles = 0;
+    // every plan of one call uses one tile size: the deep variant when it is switched on and the block reads peer memory
+    bool reads_peer = false;
+    for (int i = 0; i < n; ++i) reads_peer = reads_peer || (descs[i].flags & SH_DESC_PEER_SOURCE) != 0;
+    const int segs = (reads_peer && peer_deep_loads()) ? kDeepSegsPerThread : kSegsPerThread;
+    const int64_t tile_segs = static_cast<int64_t>(kThreads) * segs;
 
     for (int i = 0; i < n; ++i) {
         const ShParamDesc& u = descs[i];
@@ -538,6 +549,7 @@ int build_plans(const ShParamDesc* descs, int n, const void* packed, size_t pack
             if (plan != nullptr) close_plan(*plan, tiles);
             plan = &plans_out[n_plans++];
             memset(plan, 0, sizeof(BlockPlan));
+            plan->segs_per_thread = static_cast<uint32_t>(segs);
             tiles = 0;
         }
         DescDev D;
@@ -582,7 +594,7 @@ int build_plans(const ShParamDesc* descs, int n, const void* packed, size_t pack
                 if (vec) {
                     D.path = kPathDequantVec;
                     D.segs_per_row = static_cast<int32_t>(u.cols / kSegBytes);
-                    n_tiles = ceil_div(u.rows * D.segs_per_row, kTileSegs);
+                    n_tiles = ceil_div(u.rows * D.segs_per_row, tile_segs);
                     // bulk scale fetch: 16-byte aligned arrays whose 4-row padding stays inside the image
                     const int64_t rows4 = (u.rows + 3) & ~int64_t(3);
                     const bool bulk_ok = !absolute && !(D.flags & SH_DESC_PEER_SOURCE) && aligned(D.scale, 16) &&
@@ -592,7 +604,9 @@ int build_plans(const ShParamDesc* descs, int n, const void* packed, size_t pack
                     if (osz == 2 && aligned(obase + u.dst_off, 32)) D.flags |= kFlagStore32;
                     if (u.ld == u.cols) D.flags |= kFlagDense;
                     const uint64_t spr64 = static_cast<uint64_t>(D.segs_per_row);
-                    D.row_magic = ((spr64 + kTileSegs) * spr64 < (uint64_t(1) << 32)) ? ((uint64_t(1) << 32) / spr64 + 1) : 0;
+                    // valid for every in-tile index of the larger (deep) tile, hence of both
+                    D.row_magic = ((spr64 + kThreads * kDeepSegsPerThread) * spr64 < (uint64_t(1) << 32))
+                                      ? ((uint64_t(1) << 32) / spr64 + 1) : 0;
                 } else {
                     D.path = kPathDequantScalar;
                     n_tiles = ceil_div(u.rows * u.cols, kTileItems);

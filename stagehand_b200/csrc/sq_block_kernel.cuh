@@ -33,6 +33,11 @@ constexpr int kSegsPerThread  = SQ_SEGS_PER_THREAD;     // vector loads in fligh
 constexpr int kTileSegs       = kThreads * kSegsPerThread;   // 512 vectors = 8 KiB int8 -> 16 KiB bf16 per tile
 constexpr int kTileItems      = kThreads * 16;               // items per tile on the element-wise paths
 constexpr int kSmemRows       = kTileSegs + 8;               // scale rows staged per tile (worst case 1 row / vector)
+// The "deep" variant for launches that read another GPU's memory: twice the loads in flight per thread, a
+// quarter of the resident threads (4 CTAs per SM).  NVLink latency is covered by bytes in flight per thread
+// instead of by thread count, so the launch leaves most of every SM's thread slots to other kernels.
+constexpr int kDeepSegsPerThread = 8;
+constexpr int kDeepMinCtasPerSm  = 4;
 
 // how a descriptor is executed
 enum Path : int32_t {
@@ -72,7 +77,8 @@ struct BlockPlan {
     int32_t  n_desc;
     int32_t  total_tiles;
     uint32_t tile_stride;                 // CTA b works on tile (b * tile_stride) mod total_tiles; 1 = in order.
-    uint32_t pad_;                        // A stride coprime with total_tiles scatters neighbouring CTAs over the
+    uint32_t segs_per_thread;             // vector loads per thread of the dequant tiles (kSegsPerThread or kDeepSegsPerThread)
+                                          // A stride coprime with total_tiles scatters neighbouring CTAs over the
                                           // whole launch, so a launch that reads from several GPUs pulls from all
                                           // of them at once instead of one stripe (one peer) at a time.
     uint32_t tile_begin[kMaxDescs + 1];   // first tile of each descriptor; [n_desc] = total
@@ -101,5 +107,9 @@ cudaError_t launch_plan(const BlockPlan& plan, int out_dtype, cudaStream_t strea
 // Cap, in CTAs per SM, on launches that read another GPU's memory (0 = none).
 void set_peer_ctas_per_sm(int n);
 int peer_ctas_per_sm();
+
+// Whether plans that read another GPU's memory are built for the deep variant (off by default).
+void set_peer_deep_loads(bool on);
+bool peer_deep_loads();
 
 }  // namespace sq

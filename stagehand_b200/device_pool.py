@@ -116,9 +116,10 @@ class DeviceSlabPool:
 
     def release(self, slab: DeviceSlab, stream: torch.cuda.Stream | None = None) -> None:
         """Park *slab*; readers queued on *stream* (default: current) finish before its next writer starts."""
-        s = stream if stream is not None else torch.cuda.current_stream(self._device)
-        self._native.check(self._lib.sh_slab_release(self._pool, slab.slab_id, self._native.stream_handle(s)),
-                           "sh_slab_release")
+        handle = self._native.stream_handle(stream) if stream is not None else \
+            torch._C._cuda_getCurrentRawStream(self._device.index if self._device.index is not None
+                                               else torch.cuda.current_device())
+        self._native.check(self._lib.sh_slab_release(self._pool, slab.slab_id, handle), "sh_slab_release")
         if self._max_parked is not None and self._parked_bytes + slab.nbytes > self._max_parked:
             self._drop(slab.slab_id)             # the tensor goes back to the caching allocator
             return

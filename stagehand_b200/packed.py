@@ -94,6 +94,7 @@ class PackedBlockImage:
     static_ops: list[_StaticOp] = field(default_factory=list)
     dynamic_rows: list[_DynamicRow] = field(default_factory=list)
     _static_split: Any = None
+    _dynamic_split: Any = None                   # (desc_version, descriptors, n): rebuilt only when a kind changed
     last_source: dict[str, int] = field(default_factory=dict)   # dynamic row -> data_ptr of the tensor last staged
     desc_version: int = 0                        # bumped whenever a descriptor's kind or size changes (plans built
                                                  # from the descriptors, e.g. a registered block, are then stale)
@@ -184,6 +185,17 @@ class PackedBlockImage:
                     and desc.kind != SH_KIND_ZERO):
                 continue          # same tensor, not modified since it was last staged: the slot is current
             was_staged = row.staged_from == stamp and stamp is not None and desc.kind != SH_KIND_ZERO
+            if (persistent and small and was_staged and source.is_contiguous()
+                    and (source.dtype == self.runtime_dtype or source.dtype == torch.float32)):
+                # Same tensor as last time and its bytes go into the slot unconverted (the kind is already
+                # COPY or CAST_F32): compare and, if need be, copy the raw bytes in one native call instead of
+                # building views and comparing tensors.  Exact whatever way the parameter was written.
+                differs = ctypes.c_int32(0)
+                _native.check(_native.lib().sh_sync_bytes(buffer.data_ptr() + row.offset - base_offset, source.data_ptr(),
+                                                          row.numel * source.element_size(), ctypes.byref(differs)),
+                              "sh_sync_bytes")
+                changed = changed or bool(differs.value)
+                continue
             row.staged_from = stamp
             flat = source.detach().reshape(-1)
             if flat.device.type != "cpu":
@@ -225,13 +237,15 @@ class PackedBlockImage:
         if self._static_split is None:     # static descriptors never change: build their array once
             static = [self.descs[i] for i in range(self.n_descs) if i not in dyn_index]
             self._static_split = (_native.make_descs(static), len(static))
-        dynamic = []
-        for i in sorted(dyn_index):
-            d = ShParamDesc()
-            ctypes.memmove(ctypes.byref(d), ctypes.byref(self.descs[i]), ctypes.sizeof(ShParamDesc))
-            d.src_off -= self.static_bytes
-            dynamic.append(d)
-        return self._static_split[0], self._static_split[1], _native.make_descs(dynamic), len(dynamic)
+        if self._dynamic_split is None or self._dynamic_split[0] != self.desc_version:
+            dynamic = []
+            for i in sorted(dyn_index):
+                d = ShParamDesc()
+                ctypes.memmove(ctypes.byref(d), ctypes.byref(self.descs[i]), ctypes.sizeof(ShParamDesc))
+                d.src_off -= self.static_bytes
+                dynamic.append(d)
+            self._dynamic_split = (self.desc_version, _native.make_descs(dynamic), len(dynamic))
+        return self._static_split[0], self._static_split[1], self._dynamic_split[1], self._dynamic_split[2]
 
 
 def _find_param(module: nn.Module | None, dotted: str) -> nn.Parameter | None:

@@ -212,6 +212,7 @@ class StagehandScheduler:
         self._save_buffers: dict[tuple[str, str, str], torch.Tensor] = {}
         self._pending_saves: dict[str, torch.cuda.Event] = {}
         self._status_warned = False
+        self._evict_sites: dict[str, tuple[Any, list]] = {}     # block -> (module, [(name, owner, attribute, dtype, mutable)])
         self._time_blocks = bool(getattr(config, "telemetry_block_timings", False) and config.telemetry_enabled)
         self._nvtx = bool(getattr(config, "nvtx_ranges", False))
         self._stall_probes: list[tuple[Any, Any]] = []          # (before, after) timing events on the compute stream
@@ -226,6 +227,7 @@ class StagehandScheduler:
         self._block_ids = [e.block_id for e in self._ordered_blocks]
         self._index_of = {bid: i for i, bid in enumerate(self._block_ids)}
         self._view_cache: dict[tuple[str, int], list[tuple[Any, str, torch.Tensor]]] = {}
+        self._evict_sites = {}
         if getattr(self, "_image_plans", None):
             self._image_plans.clear()
         if getattr(self, "_streamer", None) is not None:
@@ -320,6 +322,8 @@ class StagehandScheduler:
 
     def _reconcile_file_backed_grads(self) -> None:
         """Mutable parameters that live on the CPU get their gradients back on the CPU at step end."""
+        if self._inference_mode:
+            return           # nothing computes gradients in an inference runtime
         for entry in self._ordered_blocks:
             if not entry.file_backed or not entry.module_param_names:
                 continue
@@ -500,7 +504,7 @@ class StagehandScheduler:
             from stagehand_b200.events import release_event
 
             done = pending.ready.done()
-            compute = torch.cuda.current_stream()
+            compute = torch._C._cuda_getCurrentRawStream(torch.cuda.current_device())   # the handle is all that is needed
             if self._nvtx:
                 torch.cuda.nvtx.range_push(f"stagehand.wait {block_id}")
             if self._time_blocks and not done:
@@ -1122,7 +1126,9 @@ class StagehandScheduler:
         self._residency.transition(block_id, BlockState.EVICTING if save_back else BlockState.GPU_FREEING)
 
         if module is not None and res.param_layout is not None:
-            if source_backed:
+            if source_backed and self._inference_mode and not self._defer_backward_eviction:
+                self._evict_source_backed_inference(block_id, module, res)
+            elif source_backed:
                 mutable = set(entry.module_param_names)
                 saved_async = False
                 keep_on_gpu = self._defer_backward_eviction and not self._backward_phase
@@ -1194,6 +1200,42 @@ class StagehandScheduler:
                             param.grad = param.grad.to("cpu")
         self._release_device_storage(res)
         self._residency.transition(block_id, BlockState.UNLOADED)
+
+    def _evict_source_backed_inference(self, block_id: str, module: nn.Module, res: "ResidencyEntry") -> None:
+        """Inference eviction of a SquareQ- or file-backed block: frozen parameters are emptied, module-owned ones
+        go back to the host copy made at their first eviction (their value cannot change while they sit in VRAM,
+        so no device-to-host read -- which would stall the host until the GPU has caught up -- is repeated).
+
+        The ``(owner module, attribute)`` of every parameter is resolved once per block and kept.
+        """
+        entry = self._registry.get(block_id)
+        sites = self._evict_sites.get(block_id)
+        if sites is None or sites[0] is not module or len(sites[1]) != len(res.param_layout):
+            mutable = set(entry.module_param_names)
+            sites = (module, [(name, *_resolve(module, name), dtype, name in mutable)
+                              for name, _shape, dtype, _off, _numel in res.param_layout])
+            self._evict_sites[block_id] = sites
+        host_copies = self._evicted_copies.setdefault(block_id, {})
+        image_plan = self._image_plans.get(block_id)
+        staged_ptrs = image_plan.last_source if image_plan is not None else {}
+        for name, owner, leaf, dtype, is_mutable in sites[1]:
+            param = getattr(owner, leaf)
+            if not is_mutable:
+                new = self._empty(dtype)
+            else:
+                live = param.data
+                kept = host_copies.get(name)
+                if (kept is not None and kept.dtype == live.dtype and kept.shape == live.shape
+                        and staged_ptrs.get(name) == kept.data_ptr()):
+                    new = kept
+                else:
+                    with torch.inference_mode(False):
+                        new = live.to("cpu").clone()
+                    host_copies[name] = new
+            try:
+                param.data = new
+            except RuntimeError:
+                setattr(owner, leaf, nn.Parameter(new, requires_grad=param.requires_grad))
 
     def _empty(self, dtype: torch.dtype) -> torch.Tensor:
         """The zero-element tensor evicted frozen parameters point at (one per dtype, shared)."""

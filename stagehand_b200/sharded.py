@@ -214,9 +214,12 @@ class DeviceImageStore:
 
     def __init__(self, runtime: Any, rank: int = 0, world: int = 1, layout: str = "owner", fused: bool = True,
                  group: Any = None, emulate_world: int = 0, peer_ctas_per_sm: int | None = None,
-                 gather: bool = False) -> None:
+                 gather: bool = False, peer_deep_loads: bool | None = None) -> None:
         if not torch.cuda.is_available():
             raise TransferError("device-resident images need a CUDA device")
+        if peer_deep_loads is not None:
+            # process-wide: blocks that read peer memory use the kernel variant with more loads in flight per thread
+            _native.check(_native.lib().sh_set_peer_deep_loads(1 if peer_deep_loads else 0), "sh_set_peer_deep_loads")
         if peer_ctas_per_sm is not None:
             # process-wide: how much of each SM a kernel that reads peer memory may occupy (0 = no cap)
             _native.check(_native.lib().sh_set_peer_ctas_per_sm(int(peer_ctas_per_sm)), "sh_set_peer_ctas_per_sm")

@@ -192,6 +192,33 @@ def test_capped_peer_launch_walks_its_tiles_grid_stride(cap: int) -> None:
         _assert_same(out[off : off + ref.size], ref, "bf16")
 
 
+@pytest.mark.parametrize("cap", [0, 1])
+def test_deep_load_variant_for_peer_sources_matches(cap: int) -> None:
+    """Blocks that read peer memory can run with 8 loads in flight per thread (tiles of 1024 vectors): same bytes,
+    one tile per CTA or walking the tiles grid-stride under a CTA cap, zero points, ragged last tiles, padded rows."""
+    rng = np.random.default_rng(29)
+    lib = _native.lib()
+    img = HandImage()
+    cases = []
+    for rows, cols, with_zp, pad in ((3000, 4096, False, 0), (1537, 2048, True, 0), (40000, 64, False, 0),
+                                     (9, 1000, True, 0), (2049, 1024, False, 64), (1, 16, False, 0)):
+        q = rng.integers(-128, 128, size=(rows, cols + pad), dtype=np.int8)
+        scale = np.exp(rng.standard_normal(rows)).astype(np.float32)
+        zp = rng.standard_normal(rows).astype(np.float32) if with_zp else None
+        cases.append((img.add_dequant(q, scale, zp, rows, cols, "bf16", peer=True), q, scale, zp, rows, cols))
+    try:
+        _native.check(lib.sh_set_peer_deep_loads(1))
+        _native.check(lib.sh_set_peer_ctas_per_sm(cap))
+        out, status = run_block(img, "bf16")
+    finally:
+        _native.check(lib.sh_set_peer_deep_loads(0))
+        _native.check(lib.sh_set_peer_ctas_per_sm(0))
+    assert status == 0
+    for off, q, scale, zp, rows, cols in cases:
+        ref = oracle.dequant_rows(q, scale, zp, rows, cols, "bf16")
+        _assert_same(out[off : off + ref.size], ref, "bf16")
+
+
 def test_bad_descriptors_are_rejected_before_launch() -> None:
     lib = _native.lib()
     _native.check(lib.sh_init(torch.cuda.current_device()))

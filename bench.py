@@ -78,9 +78,13 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--layout", default="striped", choices=["striped", "owner"],
                     help="multi-GPU: rows of every weight striped over all ranks, or whole blocks round-robin")
     ap.add_argument("--no-fused", action="store_true", help="multi-GPU, owner layout: copy-engine pull + kernel instead of the fused kernel")
-    ap.add_argument("--delivery", default="gather", choices=["gather", "fused"],
+    ap.add_argument("--delivery", default="auto", choices=["auto", "gather", "fused"],
                     help="multi-GPU, striped layout: one copy-engine pull per owner into local staging + the local "
-                         "kernel (gather), or the block kernel loading peers' memory itself (fused)")
+                         "kernel (gather), the block kernel loading peers' memory itself (fused), or per load: gather "
+                         "while blocks arrive ahead of their use, fused while the compute stream waits for them (auto)")
+    ap.add_argument("--gather-parts", type=int, default=0,
+                    help="multi-GPU gather: copies per block at least this many (owners' chunks are cut; 0 = library default)")
+    ap.add_argument("--staging-slabs", type=int, default=0, help="INT8 staging slabs in VRAM (0 = prefetch_k + 1)")
     ap.add_argument("--skip-cfg5", action="store_true", help="multi-GPU: do not append the encoder + DiT pass")
     ap.add_argument("--skip-parity", action="store_true")
     ap.add_argument("--no-wraparound", action="store_true",
@@ -222,7 +226,7 @@ def make_runtime(args, model, fpk: Path, pattern: str):
         prefetch_window_blocks=args.prefetch_k, eviction_cooldown_steps=0,
         nan_inf_check=False, strict_bf16=False, telemetry_enabled=True, telemetry_interval_steps=0,
         telemetry_file=os.devnull, packed_image_cache_mb=-1, prefetch_wraparound=not args.no_wraparound,
-        dequant_stream_priority=args.dequant_priority)
+        dequant_stream_priority=args.dequant_priority, device_staging_slabs=args.staging_slabs)
     rt = sh.StagehandRuntime(model, cfg, block_pattern=pattern, group="dit", dtype=torch.bfloat16,
                              inference_mode=True)
     converted = rt.convert_registry_to_file_backed(str(fpk))
@@ -341,13 +345,16 @@ def parity_blocks(rt) -> list[str]:
     return list(picked.values())
 
 
-def delivered_digest(rt, block_id: str, step: int) -> str:
+def delivered_digest(rt, block_id: str, step: int, force_reload: bool = False) -> str:
     """SHA-256 of *block_id*'s VRAM slab as the streaming path delivers it (loaded on demand if it is not resident)."""
     import hashlib
 
     import torch
 
     sched = rt._scheduler
+    if force_reload and rt._residency.get_state(block_id).value == "gpu_ready" \
+            and rt._residency.get_entry(block_id).refcount == 0:
+        sched._evict_block(block_id, save_back=False)
     rt.begin_step(step)
     sched.before_block(block_id)
     torch.cuda.synchronize()
@@ -399,21 +406,34 @@ def oracle_digest(rt, block_id: str, fpk: Path) -> str:
 def parity_check(rt, fpk: Path, dist_state, step: int) -> dict:
     """Digest a few delivered blocks on every rank; rank 0 also expands them with the oracle.  Outside any timed region."""
     blocks = parity_blocks(rt)
-    mine = {b: delivered_digest(rt, b, step + i) for i, b in enumerate(blocks)}
+    sched = rt._scheduler
+    views = ["gather", "fused"] if sched._delivery_mode == "auto" else [None]
+    mine: dict[str, str] = {}
+    configured = sched._delivery_mode
+    try:
+        for view in views:      # with both views on offer, each block is delivered and digested through each of them
+            if view is not None:
+                sched._delivery_mode = view
+            for i, b in enumerate(blocks):
+                mine[b if view is None else f"{b} [{view}]"] = delivered_digest(rt, b, step + i, force_reload=view is not None)
+    finally:
+        sched._delivery_mode = configured
+    keys = list(mine)
     gathered = [mine]
     if dist_state["world"] > 1:
         import torch.distributed as dist
 
         gathered = [None] * dist_state["world"]
         dist.all_gather_object(gathered, mine)
-    out = {"blocks": blocks, "ranks_equal": all(g == gathered[0] for g in gathered), "oracle_equal": None,
+    out = {"blocks": keys, "ranks_equal": all(g == gathered[0] for g in gathered), "oracle_equal": None,
            "ranks": len(gathered), "checker": "oracle.squareq_oracle.stage_block + scalar-C dequant on the host cores"}
     if dist_state["rank"] == 0:
-        expect = {b: oracle_digest(rt, b, fpk) for b in blocks}
+        by_block = {b: oracle_digest(rt, b, fpk) for b in blocks}
+        expect = {k: by_block[k.split(" [")[0]] for k in keys}
         out["oracle_equal"] = all(g == expect for g in gathered)
-        out["sha256"] = {b: expect[b][:16] for b in blocks}
+        out["sha256"] = {b: by_block[b][:16] for b in blocks}
         if not (out["ranks_equal"] and out["oracle_equal"]):
-            out["mismatch"] = [{"rank": r, "block": b} for r, g in enumerate(gathered) for b in blocks if g[b] != expect[b]]
+            out["mismatch"] = [{"rank": r, "block": k} for r, g in enumerate(gathered) for k in keys if g[k] != expect[k]]
     return out
 
 
@@ -1046,12 +1066,16 @@ def run_vmm(args) -> None:
 
 
 def kernel_profile(native, timeout_ms: int = 120_000) -> dict:
+    """Sums of the per-block timing records since the last call (outside any timed region: it drains the GPU first)."""
     import ctypes
 
-    ms, n, el, by = ctypes.c_double(0), ctypes.c_int64(0), ctypes.c_int64(0), ctypes.c_int64(0)
-    native.check(native.lib().sh_profile_collect(ctypes.byref(ms), ctypes.byref(n), ctypes.byref(el), ctypes.byref(by),
-                                                 timeout_ms), "sh_profile_collect")
-    return {"kernel_ms": ms.value, "launches": n.value, "elements": el.value, "bytes": by.value}
+    import torch
+
+    torch.cuda.synchronize()
+    sums = native.ShProfileSums()
+    native.check(native.lib().sh_profile_poll(ctypes.byref(sums)), "sh_profile_poll")
+    return {"kernel_ms": sums.kernel_ms, "launches": sums.kernel_blocks, "elements": sums.elements,
+            "bytes": sums.kernel_bytes, "copy_ms": sums.copy_ms, "copies": sums.copies, "copy_bytes": sums.copy_bytes}
 
 
 def main() -> None:
@@ -1120,7 +1144,8 @@ def main() -> None:
                 store = DeviceImageStore(rt, rank=rank, world=world, fused=not args.no_fused,
                                          layout=args.layout if world > 1 else "owner",
                                          peer_ctas_per_sm=args.peer_ctas_per_sm,
-                                         gather=args.delivery == "gather", peer_deep_loads=args.peer_deep_loads)
+                                         gather=args.delivery, peer_deep_loads=args.peer_deep_loads,
+                                         gather_parts=args.gather_parts or None)
             device_inputs = [t.cuda() for t in host_inputs]
             host_io = name == "e2e"
             step = [0]
@@ -1146,13 +1171,16 @@ def main() -> None:
                    "host_stall_ms": float(getattr(last, "stall_time_ms", 0.0)),
                    "input_bytes": sum(t.numel() * t.element_size() for t in host_inputs),
                    "setup_s": setup_phase_s,
-                   "delivery": (("gather" if store.gather else "fused") if store is not None and world > 1 else None)}
+                   "gathered_loads": last.gathered_loads,
+                   "delivery": (store.delivery if store is not None and world > 1 else None)}
             if not args.skip_delivery_only:
                 go(1, compute=False, io=False)
                 kernel_profile(native)
                 native.lib().sh_stats_reset()
                 ms_d, _ = timed_region(lambda n: go(n, compute=False, io=False), steps, dist_state, None)
-                out["delivery_only"] = {"ms_total": ms_d, "profile": kernel_profile(native), "stats": native.stats()}
+                out["delivery_only"] = {"ms_total": ms_d, "profile": kernel_profile(native), "stats": native.stats(),
+                                        "gathered_loads": rt.telemetry.last().gathered_loads,
+                                        "loads": rt.telemetry.last().dequant_launches}
             native.check(native.lib().sh_profile_enable(0))
             if not args.skip_parity:
                 out["parity"] = parity_check(rt, fpk, dist_state, step[0])
@@ -1273,7 +1301,12 @@ def compose_line(args, world: int, results: dict, peaks: dict, link_peak: float,
                                    "staging ring); the host link is not in this timed region" + ("" if world == 1 else
                                    f"; {args.layout} layout over {world} GPUs, " +
                                    ({"gather": "one copy-engine pull per owner into local staging, then the local block kernel",
-                                     "fused": "fused peer-load dequant"}[v["delivery"]] if args.layout == "striped" else
+                                     "fused": "fused peer-load dequant",
+                                     "auto": "per load: copy-engine gather + local kernel while blocks arrive ahead of "
+                                             "their use, fused peer-load dequant while the compute stream waits for them "
+                                             f"({v['gathered_loads']} of {v['stats']['kernel_launches'] // max(v['steps'], 1)} "
+                                             "loads gathered in the last timed step)"}[v["delivery"]]
+                                    if args.layout == "striped" else
                                     ("fused peer-load dequant" if not args.no_fused else "copy-engine pull + dequant"))),
                    "e2e_source": "packed INT8 images in page-locked host memory (configuration 2 as named: 8 GB budget, "
                                  "prefetch 3)" if world == 1 else
@@ -1311,7 +1344,11 @@ def compose_line(args, world: int, results: dict, peaks: dict, link_peak: float,
         line["delivery_only"] = {
             "hbm": {"value": gbs(v, d["ms_total"]), "ms_per_step": d["ms_total"] / K,
                     "kernel_hbm": kernel_roof(d["profile"], world == 1),
-                    "copies_per_step": d["stats"]["peer_copies"] / K}}
+                    "copies_per_step": d["stats"]["peer_copies"] / K,
+                    "gathered_loads_of_loads": [d.get("gathered_loads"), d.get("loads")],
+                    "copy_engine_ms_per_step": d["profile"]["copy_ms"] / K,
+                    "copy_engine_gbs_while_copying": (d["profile"]["copy_bytes"] / d["profile"]["copy_ms"] / 1e6)
+                    if d["profile"]["copy_ms"] > 0 else None}}
         if world > 1:
             line["delivery_only"]["hbm"]["nvlink_gbs_per_gpu"] = v["peer_bytes"] * K / (d["ms_total"] / 1e3) / 1e9
         if de is not None and world == 1:

@@ -201,6 +201,8 @@ class StagehandScheduler:
         self._image_plans: dict[str, "PackedBlockImage"] = {}
         self._device_sources: dict[str, Any] = {}                   # block_id -> streamer.DeviceSource
         self._device_source_fused = True
+        self._delivery_mode = "gather"                      # "gather" | "fused" | "auto" for sources that offer both views
+        self._recent_waits: list[bool] = []                 # last awaits: was the block still in flight on the device?
         self._deferred_slabs: list[tuple[Any, "PinnedSlab"]] = []   # (copied event, pool slab) awaiting DMA completion
         self._squareq_v2_loader: Any = None
         self._empties: dict[torch.dtype, torch.Tensor] = {}
@@ -504,6 +506,10 @@ class StagehandScheduler:
             from stagehand_b200.events import release_event
 
             done = pending.ready.done()
+            if self._delivery_mode == "auto":
+                self._recent_waits.append(not done)
+                if len(self._recent_waits) > 8:
+                    del self._recent_waits[0]
             compute = torch._C._cuda_getCurrentRawStream(torch.cuda.current_device())   # the handle is all that is needed
             if self._nvtx:
                 torch.cuda.nvtx.range_push(f"stagehand.wait {block_id}")
@@ -792,7 +798,8 @@ class StagehandScheduler:
             if device_src is None:
                 ticket = self._streamer.submit_from_host(plan, image, out_slab)
             else:
-                ticket = self._streamer.submit_from_device(plan, device_src, self._device_source_fused, image, out_slab)
+                ticket = self._streamer.submit_from_device(plan, device_src, self._device_source_fused, image, out_slab,
+                                                           gather=self._gather_now())
         finally:
             if self._nvtx:
                 torch.cuda.nvtx.range_pop()
@@ -806,6 +813,8 @@ class StagehandScheduler:
         self._telemetry.record_link(ticket.link_bytes)
         self._telemetry.record_peer(ticket.peer_bytes)
         self._telemetry.record_dequant_launch(ticket.launches)
+        if ticket.gathered:
+            self._telemetry.record_gathered_load()
 
     def _stage_dynamic_only(self, entry: "BlockEntry", plan: "PackedBlockImage") -> tuple["HostImage", Any]:
         """Host image that only carries the dynamic section (the static one is resident in HBM)."""
@@ -821,14 +830,34 @@ class StagehandScheduler:
             image.dirty = True
         return image, None
 
-    def set_device_sources(self, sources: dict[str, Any], fused: bool = True) -> None:
+    def set_device_sources(self, sources: dict[str, Any], fused: bool = True, delivery: str = "gather") -> None:
         """Declare blocks whose static INT8 image is resident in HBM: ``block_id -> DeviceSource``.
 
         With *fused* the block kernel reads the image in place (plain loads over NVLink
         for a peer); otherwise it is pulled into a local staging slab by a copy engine first.
+
+        *delivery* decides for sources that offer both an in-place and a gathered view (row stripes over
+        several GPUs): ``"gather"`` -- copy engines pull the peers' stripes, the kernel then reads local memory
+        only and is as short as on one GPU, so it takes the least SM time from the model's own kernels;
+        ``"fused"`` -- the kernel loads the stripes over NVLink itself, which moves more bytes per second than
+        copy engines competing with that same kernel for HBM, but holds every SM while it waits; ``"auto"`` --
+        per load: gathered while blocks arrive before they are needed (the model's kernels are the bottleneck,
+        keep the SMs for them), fused while the compute stream has to wait for blocks (delivery is the
+        bottleneck and the SMs would idle anyway).
         """
+        if delivery not in ("gather", "fused", "auto"):
+            raise ValueError(f"unknown delivery mode {delivery!r}")
         self._device_sources = dict(sources)
         self._device_source_fused = fused
+        self._delivery_mode = delivery
+        self._recent_waits = []
+
+    def _gather_now(self) -> bool:
+        """Whether the next device-sourced load takes the gathered view (see :meth:`set_device_sources`)."""
+        if self._delivery_mode != "auto":
+            return self._delivery_mode == "gather"
+        recent = self._recent_waits
+        return not recent or 2 * sum(recent) < len(recent)      # fewer than half of the last awaits found the block in flight
 
     def _reap_deferred_slabs(self, force: bool = False) -> None:
         from stagehand_b200.events import release_event

@@ -111,25 +111,33 @@ class BlockStripes:
     chunks: dict[int, tuple[int, int]] = field(default_factory=dict)   # rank -> [start, end) of this block in its arena
 
 
-def plan_gather(chunks: dict[int, tuple[int, int]], rank: int, world: int) -> tuple[dict[int, int], int, list[tuple[int, int, int, int]]]:
+def plan_gather(chunks: dict[int, tuple[int, int]], rank: int, world: int,
+                min_copies: int = 1) -> tuple[dict[int, int], int, list[tuple[int, int, int, int]]]:
     """How *rank* pulls one block's remote chunks into its staging slab.
 
     Returns ``(staging offset of each remote rank's chunk, staging bytes, copies)`` where a copy is
     ``(owner, arena offset, staging offset, bytes)``.  Chunks keep their 4 KiB alignment, so every
     address keeps the alignment it has in the arena.  Copies are ordered rank+1, rank+2, ...: ranks that
-    run in step then pull from different owners at any one moment.
+    run in step then pull from different owners at any one moment.  With fewer owners than *min_copies*
+    every chunk is cut into equal 4 KiB-aligned parts, so that two copy engines have something to share.
     """
     offsets: dict[int, int] = {}
     copies: list[tuple[int, int, int, int]] = []
     cursor = 0
-    for step in range(1, world):
-        owner = (rank + step) % world
-        start, end = chunks.get(owner, (0, 0))
-        if end <= start:
-            continue
+    owners = [(rank + step) % world for step in range(1, world)]
+    owners = [o for o in owners if chunks.get(o, (0, 0))[1] > chunks.get(o, (0, 0))[0]]
+    parts = max(1, -(-int(min_copies) // max(len(owners), 1)))
+    for owner in owners:
+        start, end = chunks[owner]
         offsets[owner] = cursor
-        copies.append((owner, start, cursor, end - start))
-        cursor = _up(cursor + (end - start), _ALIGN)
+        size = end - start
+        part = _up(-(-size // parts), _ALIGN)
+        at = 0
+        while at < size:
+            n = min(part, size - at)
+            copies.append((owner, start + at, cursor + at, n))
+            at += n
+        cursor = _up(cursor + size, _ALIGN)
     return offsets, cursor, copies
 
 
@@ -214,7 +222,7 @@ class DeviceImageStore:
 
     def __init__(self, runtime: Any, rank: int = 0, world: int = 1, layout: str = "owner", fused: bool = True,
                  group: Any = None, emulate_world: int = 0, peer_ctas_per_sm: int | None = None,
-                 gather: bool = False, peer_deep_loads: bool | None = None) -> None:
+                 gather: bool | str = False, peer_deep_loads: bool | None = None, gather_parts: int | None = None) -> None:
         if not torch.cuda.is_available():
             raise TransferError("device-resident images need a CUDA device")
         if peer_deep_loads is not None:
@@ -232,7 +240,13 @@ class DeviceImageStore:
         if self._emulated:
             rank, world = 0, emulate_world
         self.rank, self.world, self.fused, self.layout = rank, world, fused, layout
-        self.gather = bool(gather) and layout == "striped" and world > 1
+        # gather: False = the block kernel reads the stripes in place; True = copy engines gather them first;
+        # "auto" = per load, whichever suits the moment (see StagehandScheduler.set_device_sources)
+        if gather not in (True, False, "auto", "gather", "fused"):
+            raise ValueError(f"unknown gather mode {gather!r}")
+        self.delivery = {True: "gather", False: "fused"}.get(gather, gather) if layout == "striped" and world > 1 else "fused"
+        self.gather = self.delivery != "fused"          # whether the gathered view is built at all
+        self.gather_parts = int(gather_parts) if gather_parts else 2      # at least two copies per block: two copy engines
         self._runtime = runtime
         sched = runtime._scheduler
         sched._ensure_int8_path()
@@ -261,9 +275,9 @@ class DeviceImageStore:
             self._exchange_handles(group)
 
         sources = self._sources()
-        sched.set_device_sources(sources, fused=fused or layout == "striped")
+        sched.set_device_sources(sources, fused=fused or layout == "striped", delivery=self.delivery)
         largest = max((p.total_bytes for p in self._plans.values()), default=_ALIGN)
-        largest = max([largest] + [src.span_bytes for src in sources.values() if src.pieces])
+        largest = max([largest] + [src.gather_span for src in sources.values() if src.pieces])
         sched._streamer.ensure_staging(largest)
 
     # ── planning ─────────────────────────────────────────────────────
@@ -337,7 +351,6 @@ class DeviceImageStore:
                                                  peer_bytes=nbytes if remote else 0)
             return sources
         for block_id, bs in self.stripes.items():
-            rows = []
             # Stripes stay grouped by weight (so a launch reads from several owners at once), but inside each
             # weight every consumer starts with a different owner (rank+1, rank+2, ..., itself last): ranks
             # running in step then do not all queue on the same GPU's egress.
@@ -346,29 +359,40 @@ class DeviceImageStore:
                 groups.setdefault(d.weight, []).append(d)
             rotated = [d for _w, ds in sorted(groups.items())
                        for d in sorted(ds, key=lambda d: (d.rank - self.rank - 1) % self.world)]
-            staged_at, staging_bytes, copies = plan_gather(bs.chunks, self.rank, self.world) if self.gather else ({}, 0, [])
-            for d in rotated:
-                if d.kind == SH_KIND_ZERO:
-                    base, flags = 0, 0
-                elif self.gather and d.rank != self.rank:
-                    # pulled into the staging slab first: an offset into that slab, read with local loads
-                    base, flags = staged_at[d.rank] - bs.chunks[d.rank][0], 0
-                else:
-                    base = self._arenas.get(d.rank, 0)
-                    flags = SH_DESC_ABSOLUTE | (SH_DESC_PEER_SOURCE if d.rank != self.rank else 0)
-                sourced = d.kind != SH_KIND_ZERO
-                rows.append(ShParamDesc(
-                    kind=d.kind, flags=flags, src_off=base + d.src_off if sourced else 0,
-                    scale_off=base + d.scale_off if d.kind == SH_KIND_DEQUANT_I8 else 0,
-                    zp_off=(base + d.zp_off) if d.zp_off >= 0 else -1, dst_off=d.dst_off, rows=d.rows, cols=d.cols, ld=d.ld))
+
+            def rows_for(gathered: bool, staged_at: dict[int, int]) -> list[ShParamDesc]:
+                rows = []
+                for d in rotated:
+                    if d.kind == SH_KIND_ZERO:
+                        base, flags = 0, 0
+                    elif gathered and d.rank != self.rank:
+                        # pulled into the staging slab first: an offset into that slab, read with local loads
+                        base, flags = staged_at[d.rank] - bs.chunks[d.rank][0], 0
+                    else:
+                        base = self._arenas.get(d.rank, 0)
+                        flags = SH_DESC_ABSOLUTE | (SH_DESC_PEER_SOURCE if d.rank != self.rank and not gathered else 0)
+                    sourced = d.kind != SH_KIND_ZERO
+                    rows.append(ShParamDesc(
+                        kind=d.kind, flags=flags, src_off=base + d.src_off if sourced else 0,
+                        scale_off=base + d.scale_off if d.kind == SH_KIND_DEQUANT_I8 else 0,
+                        zp_off=(base + d.zp_off) if d.zp_off >= 0 else -1, dst_off=d.dst_off, rows=d.rows, cols=d.cols,
+                        ld=d.ld))
+                return rows
+
+            in_place = rows_for(False, {})
             remote_bytes = sum(p.nbytes for p in bs.pieces if p.rank != self.rank)
-            pieces = [(self._arenas[owner] + at, staged, nbytes) for owner, at, staged, nbytes in copies] or None
-            if pieces:
-                remote_bytes = sum(nbytes for _s, _o, nbytes in pieces)     # whole chunks travel, padding included
-            sources[block_id] = DeviceSource(ptr=self._arenas[self.rank], is_peer=False, descs=_native.make_descs(rows),
-                                             n_descs=len(rows),
-                                             span_bytes=staging_bytes if pieces else max(self.arena_bytes[self.rank], _ALIGN),
-                                             peer_bytes=remote_bytes, pieces=pieces)
+            source = DeviceSource(ptr=self._arenas[self.rank], is_peer=False, descs=_native.make_descs(in_place),
+                                  n_descs=len(in_place), span_bytes=max(self.arena_bytes[self.rank], _ALIGN),
+                                  peer_bytes=remote_bytes)
+            if self.gather:
+                staged_at, staging_bytes, copies = plan_gather(bs.chunks, self.rank, self.world, self.gather_parts)
+                if copies:
+                    gathered = rows_for(True, staged_at)
+                    source.pieces = [(self._arenas[owner] + at, staged, nbytes) for owner, at, staged, nbytes in copies]
+                    source.gather_descs, source.n_gather_descs = _native.make_descs(gathered), len(gathered)
+                    source.gather_span = staging_bytes
+                    source.gather_peer_bytes = sum(nbytes for _o, _a, _s, nbytes in copies)   # whole chunks, padding included
+            sources[block_id] = source
         return sources
 
     def resident_bytes(self) -> int:
@@ -418,7 +442,7 @@ def park_images_in_hbm(runtime: Any, fused: bool = True) -> DeviceImageStore:
 
 
 def shard_images_over_ranks(runtime: Any, fused: bool = True, layout: str = "striped", group: Any = None,
-                            gather: bool = False) -> DeviceImageStore:
+                            gather: bool | str = "auto") -> DeviceImageStore:
     """One process per GPU: shard the INT8 images over the ranks of *group* (default: the world group)."""
     import torch.distributed as dist
 

@@ -124,11 +124,15 @@ class DeviceSource:
 
     ptr: int
     is_peer: bool = False
-    descs: Any = None             # ctypes array of ShParamDesc
+    descs: Any = None             # ctypes array of ShParamDesc: the in-place (fused) view
     n_descs: int = 0
-    span_bytes: int = 0           # bytes addressable through offset (non-absolute) descriptors
+    span_bytes: int = 0           # bytes addressable through offset (non-absolute) descriptors of `descs`
     peer_bytes: int = 0           # bytes this consumer reads from other GPUs per load
-    pieces: Any = None            # list of (source address, offset in the staging slab, bytes)
+    pieces: Any = None            # gathered view: list of (source address, offset in the staging slab, bytes) ...
+    gather_descs: Any = None      # ... and the descriptors that expand the staging slab (own stripes stay absolute)
+    n_gather_descs: int = 0
+    gather_span: int = 0          # staging bytes the gathered view needs
+    gather_peer_bytes: int = 0    # bytes the copies move (whole chunks, padding included)
 
 
 @dataclass
@@ -142,6 +146,7 @@ class StreamTicket:
     peer_bytes: int = 0
     launches: int = 0
     host_slab: Any = None         # pool slab to give back once `copied` is done (uncached images)
+    gathered: bool = False        # peers' bytes were pulled by copy engines (not loaded by the kernel itself)
 
 
 @dataclass
@@ -302,7 +307,7 @@ class Int8BlockStreamer:
         return StreamTicket(block_id, ready, None, link_bytes=nbytes, launches=0)
 
     def submit_from_device(self, image: PackedBlockImage, source: DeviceSource, fused: bool,
-                           dynamic_host: HostImage | None, out_slab: DeviceSlab) -> StreamTicket:
+                           dynamic_host: HostImage | None, out_slab: DeviceSlab, gather: bool = True) -> StreamTicket:
         """Image whose static section is resident in HBM (this GPU's, or peers' over NVLink).
 
         ``fused=True``: the block kernel reads the INT8 rows where they are (plain peer loads when that is
@@ -311,13 +316,17 @@ class Int8BlockStreamer:
         the kernel reads local memory only.  The dynamic section (live module-owned parameters), if any,
         comes from local host memory (*dynamic_host* holds that section only): it is kept in a small device
         buffer, copied again only when the host staged something new, and its descriptors ride in the same
-        launch as the static ones.
+        launch as the static ones.  A source that offers both views (stripes readable in place and as
+        gather pieces) is loaded through the gathered one when *gather* is true.
         """
         static_descs, n_static, dyn_descs, n_dyn = image.split_descs()
         pieces = None
-        if source.descs is not None:
+        if source.descs is not None and source.pieces and gather:
+            static_descs, n_static, span = source.gather_descs, source.n_gather_descs, max(source.gather_span, 1)
+            pieces, peer_bytes = source.pieces, source.gather_peer_bytes
+        elif source.descs is not None:
             static_descs, n_static, span = source.descs, source.n_descs, max(source.span_bytes, 1)
-            pieces, peer_bytes = source.pieces, source.peer_bytes
+            peer_bytes = source.peer_bytes
         else:
             span = max(image.static_bytes, 1)
             peer_bytes = image.static_bytes if source.is_peer else 0
@@ -356,7 +365,8 @@ class Int8BlockStreamer:
 
         stamp = (id(image), image.desc_version, id(source), bool(pieces), dyn.buffer.data_ptr() if dyn else 0,
                  bool(fused))
-        reg = self._registered.get((image.block_id, "device"))
+        key = (image.block_id, "gather" if pieces else "device")
+        reg = self._registered.get(key)
         if reg is None or reg.stamp != stamp:
             rows = []
             for i in range(n_static):
@@ -373,7 +383,7 @@ class Int8BlockStreamer:
                     d.src_off += dyn.buffer.data_ptr()
                 rows.append(d)
             merged = _native.make_descs(rows)
-            reg = self._register((image.block_id, "device"), stamp, merged, len(rows), span, image.out_bytes,
+            reg = self._register(key, stamp, merged, len(rows), span, image.out_bytes,
                                  image.out_dtype_code, pieces=pieces, keepalive=(image, source, merged))
 
         what = f"sh_block_load({image.block_id})"
@@ -390,7 +400,7 @@ class Int8BlockStreamer:
             self._load(reg, what, src=source.ptr, kind=_native.SH_SRC_DEVICE, staging=0, out_slab=out_slab,
                        src_ready=src_ready, ready=ready.handle, ready3=ready3)
         return StreamTicket(image.block_id, ready, copied, link_bytes=link_bytes, peer_bytes=peer_bytes,
-                            launches=reg.launches)
+                            launches=reg.launches, gathered=bool(pieces))
 
     # ── status ───────────────────────────────────────────────────────
 

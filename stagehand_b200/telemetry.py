@@ -55,6 +55,7 @@ class StepMetrics:
     dequant_time_ms: float = 0.0     # device time of the block kernel, summed over the blocks harvested this step
     exposed_stall_ms: float = 0.0    # device time the compute stream spent waiting for a block's ready event
     timed_blocks: int = 0            # blocks whose kernel time is in dequant_time_ms
+    gathered_loads: int = 0          # loads whose peer bytes were pulled by copy engines (the others read them in place)
 
 
 class StagehandTelemetry:
@@ -105,6 +106,9 @@ class StagehandTelemetry:
 
     def record_dequant_launch(self, n: int = 1) -> None:
         self._bump(dequant_launches=n)
+
+    def record_gathered_load(self) -> None:
+        self._bump(gathered_loads=1)
 
     def record_image_cache_hit(self) -> None:
         self._bump(image_cache_hits=1)

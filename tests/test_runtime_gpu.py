@@ -152,8 +152,9 @@ def test_resident_blocks_are_hits_on_later_steps(tmp_path: Path) -> None:
 
 @pytest.mark.parametrize("layout,fused,world,gather", [("owner", True, 3, False), ("owner", False, 3, False),
                                                       ("striped", True, 3, False), ("striped", True, 8, False),
-                                                      ("striped", True, 2, True), ("striped", True, 8, True)])
-def test_sharded_layouts_emulated_on_one_gpu(layout: str, fused: bool, world: int, gather: bool, tmp_path: Path) -> None:
+                                                      ("striped", True, 2, True), ("striped", True, 8, True),
+                                                      ("striped", True, 3, "auto")])
+def test_sharded_layouts_emulated_on_one_gpu(layout: str, fused: bool, world: int, gather, tmp_path: Path) -> None:
     """One process plays every rank: arenas for all ranks on this GPU, peers read through the plain-load path.
 
     Bit-exact block images and the forward within tolerance, for the owner layout (fused and copy-engine
@@ -189,9 +190,29 @@ def test_sharded_layouts_emulated_on_one_gpu(layout: str, fused: bool, world: in
         y2 = model(x)
     torch.cuda.synchronize()
     assert torch.equal(y, y2) and rt._scheduler._streamer.read_status() == 0
-    if gather:
+    if gather is True:
         from stagehand_b200 import _native
         assert _native.stats()["peer_copies"] >= (world - 1) * 4
+    if gather == "auto":
+        # both views of the same stripes: force each in turn and reload a block through it
+        sched = rt._scheduler
+        entry = rt._registry.blocks_in_order()[1]
+        want = str(G["cfg1__block_sha256"][1])
+        for view, gathered_loads in (("gather", 1), ("fused", 0)):
+            sched._delivery_mode = view
+            if rt._residency.get_state(entry.block_id) is sh.BlockState.GPU_READY:
+                sched._evict_block(entry.block_id)
+            rt.begin_step(5)
+            sched.before_block(entry.block_id)
+            torch.cuda.synchronize()
+            img = rt._residency.get_entry(entry.block_id).gpu_tensor.view(torch.uint8).cpu().numpy()
+            assert hashlib.sha256(img.tobytes()).hexdigest() == want, view
+            sched.after_block(entry.block_id)
+            # loads in this step: the block itself plus whatever the window prefetched, all through one view
+            m2 = rt._telemetry._current
+            assert (m2.gathered_loads > 0) == bool(gathered_loads) and m2.dequant_launches >= 1
+            rt.end_step()
+        sched._delivery_mode = "auto"
     rt.end_step()
     rt.shutdown()
     store.close()

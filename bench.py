@@ -1171,7 +1171,8 @@ def main() -> None:
                    "host_stall_ms": float(getattr(last, "stall_time_ms", 0.0)),
                    "input_bytes": sum(t.numel() * t.element_size() for t in host_inputs),
                    "setup_s": setup_phase_s,
-                   "gathered_loads": last.gathered_loads,
+                   "gathered_loads": last.gathered_loads, "probed_blocks": last.probed_blocks,
+                   "on_time_blocks": last.on_time_blocks, "exposed_stall_ms": last.exposed_stall_ms,
                    "delivery": (store.delivery if store is not None and world > 1 else None)}
             if not args.skip_delivery_only:
                 go(1, compute=False, io=False)
@@ -1288,7 +1289,8 @@ def compose_line(args, world: int, results: dict, peaks: dict, link_peak: float,
                     "peak_source": nvlink_probe["peak_source"], "nominal_peak": nvlink_probe["nominal_gbs"],
                     "kernel_hbm": kernel_roof(v["profile"], False)}
 
-    telemetry_keys = ("hits", "soft_hits", "misses", "evictions", "host_stall_ms", "kernel_status", "vram_pool")
+    telemetry_keys = ("hits", "soft_hits", "misses", "evictions", "host_stall_ms", "kernel_status", "vram_pool",
+                      "gathered_loads", "probed_blocks", "on_time_blocks", "exposed_stall_ms")
     line = {
         "metric": METRIC, "value": gbs(v, v["ms_total"]), "unit": UNIT, "n_gpus": world, "steps": K,
         "warmup": args.warmup, "ms_per_step": v["ms_total"] / K, "higher_is_better": True, "scaling": "weak",
@@ -1334,7 +1336,8 @@ def compose_line(args, world: int, results: dict, peaks: dict, link_peak: float,
                       "exposed_delivery_ms": max(0.0, (e["ms_total"] - v["ms_total"]) / K),
                       "note": "a block found in flight counts as a miss, as in the reference (its before_block), even when "
                               "nothing waited: on a link-bound pass every block is in flight at use, so hit_rate says "
-                              "nothing here; host_stall_ms and exposed_delivery_ms are the health signals"},
+                              "nothing here; host_stall_ms, exposed_delivery_ms and, where waits are timed on the device "
+                              "(automatic delivery at N > 1), on_time_blocks / probed_blocks are the health signals"},
         "setup_s": setup_s,
     }
     if world > 1:

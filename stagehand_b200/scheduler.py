@@ -218,6 +218,9 @@ class StagehandScheduler:
         self._time_blocks = bool(getattr(config, "telemetry_block_timings", False) and config.telemetry_enabled)
         self._nvtx = bool(getattr(config, "nvtx_ranges", False))
         self._stall_probes: list[tuple[Any, Any]] = []          # (before, after) timing events on the compute stream
+        self._exposed_ms = 0.0                                  # harvested probe time not yet handed to the telemetry
+        self._probed_blocks = self._on_time_blocks = 0          # harvested probes / those that found their block on time
+        self._awaits = 0
         self._timing_events: list[Any] = []                     # recycled timing events
 
     # ── step lifecycle ───────────────────────────────────────────────
@@ -259,7 +262,14 @@ class StagehandScheduler:
 
     def _harvest_device_times(self) -> None:
         """Fill the step's device-side times from events that have completed; nothing here waits."""
-        if not self._time_blocks or self._streamer is None:
+        if self._streamer is None:
+            return
+        if not self._time_blocks:
+            if self._stall_probes or self._probed_blocks:       # automatic delivery places wait probes of its own
+                self._harvest_stall_probes()
+                self._telemetry.record_device_times(exposed_stall_ms=self._exposed_ms, probed_blocks=self._probed_blocks,
+                                                    on_time_blocks=self._on_time_blocks)
+                self._exposed_ms, self._probed_blocks, self._on_time_blocks = 0.0, 0, 0
             return
         import ctypes
 
@@ -267,17 +277,37 @@ class StagehandScheduler:
 
         sums = _native.ShProfileSums()
         _native.check(_native.lib().sh_profile_poll(ctypes.byref(sums)), "sh_profile_poll")
-        exposed = 0.0
-        keep = []
-        for before, after in self._stall_probes:
-            if after.done():
-                exposed += before.elapsed_ms(after)
-                self._timing_events += [before, after]
-            else:
-                keep.append((before, after))
-        self._stall_probes = keep
+        self._harvest_stall_probes()
+        exposed, self._exposed_ms = self._exposed_ms, 0.0
         self._telemetry.record_device_times(copy_ms=float(sums.copy_ms), dequant_ms=float(sums.kernel_ms),
-                                            exposed_stall_ms=exposed, timed_blocks=int(sums.kernel_blocks))
+                                            exposed_stall_ms=exposed, timed_blocks=int(sums.kernel_blocks),
+                                            probed_blocks=self._probed_blocks, on_time_blocks=self._on_time_blocks)
+        self._probed_blocks = self._on_time_blocks = 0
+
+    # a wait on the compute stream longer than this means the block was not there when its turn came
+    _EXPOSED_WAIT_MS = 0.05
+    # automatic delivery times the wait of every n-th block only: each probe is two timing events on the compute stream
+    _PROBE_EVERY = 2
+
+    def _harvest_stall_probes(self) -> None:
+        """Read the wait probes that have completed (oldest first, stops at the first one still pending)."""
+        probes = self._stall_probes
+        n = 0
+        for before, after in probes:
+            if not after.done():
+                break
+            ms = before.elapsed_ms(after)
+            self._exposed_ms += ms
+            self._probed_blocks += 1
+            self._on_time_blocks += ms <= self._EXPOSED_WAIT_MS
+            if self._delivery_mode == "auto":
+                self._recent_waits.append(ms > self._EXPOSED_WAIT_MS)
+            self._timing_events += [before, after]
+            n += 1
+        if n:
+            del probes[:n]
+            if len(self._recent_waits) > 8:
+                del self._recent_waits[: len(self._recent_waits) - 8]
 
     def _check_kernel_status(self) -> None:
         """Look at the block kernel's status word once per step, without waiting for the GPU.
@@ -506,15 +536,14 @@ class StagehandScheduler:
             from stagehand_b200.events import release_event
 
             done = pending.ready.done()
-            if self._delivery_mode == "auto":
-                self._recent_waits.append(not done)
-                if len(self._recent_waits) > 8:
-                    del self._recent_waits[0]
             compute = torch._C._cuda_getCurrentRawStream(torch.cuda.current_device())   # the handle is all that is needed
             if self._nvtx:
                 torch.cuda.nvtx.range_push(f"stagehand.wait {block_id}")
-            if self._time_blocks and not done:
-                # how long the compute stream sits at the wait: two timing events around it, read at step end
+            self._awaits += 1
+            if (self._delivery_mode == "auto" and self._awaits % self._PROBE_EVERY == 0) or (self._time_blocks and not done):
+                # How long the compute stream sits at the wait: two timing events around it, read later without
+                # waiting.  (Whether the block is complete *now* says little: the host runs ahead of the device.)
+                self._harvest_stall_probes()
                 before, after = self._timing_event().record(compute), self._timing_event()
                 pending.ready.block_stream(compute)
                 self._stall_probes.append((before, after.record(compute)))
@@ -843,7 +872,8 @@ class StagehandScheduler:
         copy engines competing with that same kernel for HBM, but holds every SM while it waits; ``"auto"`` --
         per load: gathered while blocks arrive before they are needed (the model's kernels are the bottleneck,
         keep the SMs for them), fused while the compute stream has to wait for blocks (delivery is the
-        bottleneck and the SMs would idle anyway).
+        bottleneck and the SMs would idle anyway).  "Has to wait" is measured on the device: timing events
+        around each wait on the compute stream, read a few blocks later without blocking.
         """
         if delivery not in ("gather", "fused", "auto"):
             raise ValueError(f"unknown delivery mode {delivery!r}")
@@ -857,7 +887,7 @@ class StagehandScheduler:
         if self._delivery_mode != "auto":
             return self._delivery_mode == "gather"
         recent = self._recent_waits
-        return not recent or 2 * sum(recent) < len(recent)      # fewer than half of the last awaits found the block in flight
+        return not recent or 2 * sum(recent) < len(recent)      # fewer than half of the last blocks kept the compute stream waiting
 
     def _reap_deferred_slabs(self, force: bool = False) -> None:
         from stagehand_b200.events import release_event

@@ -4,7 +4,9 @@
 with its meaning: ``h2d_bytes`` stays "runtime-dtype bytes that became valid in
 VRAM" (what the reference counts, ``scheduler.py:951``).  What actually crossed the
 link on the INT8 path is reported in the added ``link_bytes`` / ``peer_bytes``
-fields, and the block kernel's launches in ``dequant_launches``.  With
+fields, and the block kernel's launches in ``dequant_launches``.  ``probed_blocks`` / ``on_time_blocks``
+(and :meth:`StagehandTelemetry.on_time_rate`) say how many in-flight blocks were complete when the compute
+stream reached them, measured on the device.  With
 ``StagehandConfig.telemetry_block_timings`` three device-side times are filled from CUDA events that
 are only ever *queried*, never waited for: ``copy_time_ms`` (the reference declares this field and
 never fills it, ``telemetry.py:31``), ``dequant_time_ms`` and ``exposed_stall_ms``; an event that has
@@ -56,6 +58,8 @@ class StepMetrics:
     exposed_stall_ms: float = 0.0    # device time the compute stream spent waiting for a block's ready event
     timed_blocks: int = 0            # blocks whose kernel time is in dequant_time_ms
     gathered_loads: int = 0          # loads whose peer bytes were pulled by copy engines (the others read them in place)
+    probed_blocks: int = 0           # in-flight blocks whose wait on the compute stream was timed (and has been read)
+    on_time_blocks: int = 0          # ... of which the compute stream waited less than 0.05 ms: delivered in time
 
 
 class StagehandTelemetry:
@@ -114,9 +118,17 @@ class StagehandTelemetry:
         self._bump(image_cache_hits=1)
 
     def record_device_times(self, copy_ms: float = 0.0, dequant_ms: float = 0.0, exposed_stall_ms: float = 0.0,
-                            timed_blocks: int = 0) -> None:
+                            timed_blocks: int = 0, probed_blocks: int = 0, on_time_blocks: int = 0) -> None:
         self._bump(copy_time_ms=copy_ms, dequant_time_ms=dequant_ms, exposed_stall_ms=exposed_stall_ms,
-                   timed_blocks=timed_blocks)
+                   timed_blocks=timed_blocks, probed_blocks=probed_blocks, on_time_blocks=on_time_blocks)
+
+    def on_time_rate(self) -> float:
+        """Of the in-flight blocks whose wait was timed on the device, the share that arrived in time (rolling window).
+
+        The health signal of a streamed pass: ``hit_rate`` counts a block found in flight as a miss, as the
+        reference does, even when the device never waited for it."""
+        probed = sum(m.probed_blocks for m in self._history)
+        return sum(m.on_time_blocks for m in self._history) / probed if probed else 0.0
 
     def record_stall(self, duration_ms: float) -> None:
         self._bump(stall_time_ms=duration_ms, stall_count=1)

@@ -649,6 +649,8 @@ def run_kernel_sweep(args) -> None:
             native.check(lib.sh_stream_block_async(descs, 1, host.data_ptr(), nbytes, staging.data_ptr(), out.data_ptr(),
                                                    n * k * 2, 0, stream, stream, 0, 0, None), "sh_stream_block_async")
 
+        spread = {}
+
         def timeit(fn):
             for _ in range(max(args.warmup, 1)):
                 fn()
@@ -661,6 +663,7 @@ def run_kernel_sweep(args) -> None:
                 e1.record()
                 torch.cuda.synchronize()
                 ts.append(e0.elapsed_time(e1))
+            spread[fn.__name__] = [min(ts), max(ts)]
             return statistics.median(ts)
 
         ms_res, ms_host = timeit(resident), timeit(from_host)
@@ -694,7 +697,8 @@ def run_kernel_sweep(args) -> None:
                          "burst32_hbm_frac": gbs_burst / peaks["hbm_gbs"], "burst32_distinct_buffers": copies,
                          "h2d_dequant_ms": ms_host, "h2d_only_ms": ms_copy, "link_gbs": nbytes / ms_host / 1e6,
                          "link_frac": nbytes / ms_host / 1e6 / link_peak,
-                         "link_frac_copy_only": nbytes / ms_copy / 1e6 / link_peak, "bit_exact_vs_torch": exact})
+                         "link_frac_copy_only": nbytes / ms_copy / 1e6 / link_peak, "bit_exact_vs_torch": exact,
+                         "min_max_ms": spread})
         del img, out, host, staging, ref, imgs, outs
     print(json.dumps({"metric": "dequant_kernel_sweep", "unit": "GB/s", "hbm_peak_gbs": peaks["hbm_gbs"],
                       "hbm_peak_source": peaks["source"], "host_link_peak_gbs": link_peak, "steps": args.steps,

@@ -642,11 +642,16 @@ def run_kernel_sweep(args) -> None:
             native.check(lib.sh_dequant_block_async(descs, 1, img.data_ptr(), nbytes, out.data_ptr(), n * k * 2, 0,
                                                     stream, None), "sh_dequant_block_async")
 
-        host = img.cpu().pin_memory()
+        # the host image lives where the streaming path keeps its images: in the library's own page-locked allocation
+        host_ptr = ctypes.c_void_p()
+        native.check(lib.sh_host_alloc(nbytes, ctypes.byref(host_ptr)), "sh_host_alloc")
+        pageable = img.cpu()
+        ctypes.memmove(host_ptr, pageable.data_ptr(), nbytes)
+        del pageable
         staging = torch.empty_like(img)
 
         def from_host():
-            native.check(lib.sh_stream_block_async(descs, 1, host.data_ptr(), nbytes, staging.data_ptr(), out.data_ptr(),
+            native.check(lib.sh_stream_block_async(descs, 1, host_ptr, nbytes, staging.data_ptr(), out.data_ptr(),
                                                    n * k * 2, 0, stream, stream, 0, 0, None), "sh_stream_block_async")
 
         spread = {}
@@ -687,7 +692,7 @@ def run_kernel_sweep(args) -> None:
         ms_burst = timeit(burst) / 32
         # the host link alone for the same bytes (what H2D + dequant can at best equal)
         def copy_only():
-            native.check(lib.sh_copy_h2d_async(staging.data_ptr(), host.data_ptr(), nbytes, stream), "sh_copy_h2d_async")
+            native.check(lib.sh_copy_h2d_async(staging.data_ptr(), host_ptr, nbytes, stream), "sh_copy_h2d_async")
 
         ms_copy = timeit(copy_only)
         gbs = 3.0 * n * k / ms_res / 1e6
@@ -699,7 +704,9 @@ def run_kernel_sweep(args) -> None:
                          "link_frac": nbytes / ms_host / 1e6 / link_peak,
                          "link_frac_copy_only": nbytes / ms_copy / 1e6 / link_peak, "bit_exact_vs_torch": exact,
                          "min_max_ms": spread})
-        del img, out, host, staging, ref, imgs, outs
+        torch.cuda.synchronize()
+        lib.sh_host_free(host_ptr)
+        del img, out, staging, ref, imgs, outs
     print(json.dumps({"metric": "dequant_kernel_sweep", "unit": "GB/s", "hbm_peak_gbs": peaks["hbm_gbs"],
                       "hbm_peak_source": peaks["source"], "host_link_peak_gbs": link_peak, "steps": args.steps,
                       "warmup": args.warmup, "l2": "256 MiB written between timed iterations", "shapes": rows_out}),

@@ -363,3 +363,58 @@ def test_sharded_safetensors_writer_is_read_back_by_the_safetensors_library(tmp_
     a, b = seen["blocks.0.attn_q.base.weight"], seen["blocks.2.cross_o.base.weight"]
     assert a.dtype == torch.bfloat16 and tuple(a.shape) == (32, 32) and torch.equal(a, b)      # one draw per shape
     assert tuple(seen["blocks.1.fc1.weight"].shape) == (64, 32)
+
+
+def test_delivery_choice_follows_the_device_side_wait_probes(tmp_path: Path) -> None:
+    """Sources that offer both views: gather while blocks arrive in time, fused while the compute stream waits."""
+    torch.manual_seed(0)
+    model = TinyBlockModel(n_blocks=2, hidden=64, heads=2, mlp=128)
+    rt = sh.StagehandRuntime(model, sh.StagehandConfig(pinned_pool_mb=8, pinned_slab_mb=4, telemetry_enabled=False),
+                             block_pattern=BLOCK_PATTERNS["tiny"], dtype=torch.bfloat16, inference_mode=True)
+    sched = rt._scheduler
+    with pytest.raises(ValueError):
+        sched.set_device_sources({}, delivery="sometimes")
+    sched.set_device_sources({}, delivery="gather")
+    assert sched._gather_now()
+    sched.set_device_sources({}, delivery="fused")
+    assert not sched._gather_now()
+    sched.set_device_sources({}, delivery="auto")
+    assert sched._gather_now()                                  # no probe read yet: keep the SMs free
+    sched._recent_waits[:] = [False] * 5 + [True] * 3           # 3 of the last 8 probed blocks kept the stream waiting
+    assert sched._gather_now()
+    sched._recent_waits[:] = [False] * 4 + [True] * 4           # half of them: delivery is the bottleneck
+    assert not sched._gather_now()
+    sched.set_device_sources({}, delivery="auto")               # a new set of sources starts from scratch
+    assert sched._recent_waits == [] and sched._gather_now()
+    rt.shutdown()
+
+
+def test_on_time_rate_and_device_time_fields() -> None:
+    from stagehand_b200.telemetry import StagehandTelemetry
+
+    t = StagehandTelemetry(enabled=True, interval_steps=0, output_file=None)
+    assert t.on_time_rate() == 0.0
+    for step, (probed, on_time) in enumerate([(10, 10), (10, 5)]):
+        t.begin_step(step)
+        t.record_device_times(copy_ms=2.0, dequant_ms=1.0, exposed_stall_ms=0.5, timed_blocks=4, probed_blocks=probed,
+                              on_time_blocks=on_time)
+        t.record_gathered_load()
+        t.record_link(4_000_000)
+        t.end_step()
+    last = t.last()
+    assert (last.copy_time_ms, last.dequant_time_ms, last.exposed_stall_ms, last.timed_blocks) == (2.0, 1.0, 0.5, 4)
+    assert last.gathered_loads == 1 and t.on_time_rate() == 0.75
+    assert "copy=2.0ms" in t._format_log_line(last) and "GB/s" in t._format_log_line(last)
+
+
+def test_gather_plan_splits_chunks_when_there_are_fewer_owners_than_copies() -> None:
+    from stagehand_b200.sharded import plan_gather
+
+    chunks = {0: (0, 10_000), 1: (8192, 8192 + 1_000_000)}
+    staged_at, nbytes, copies = plan_gather(chunks, rank=0, world=2, min_copies=4)
+    assert list(staged_at) == [1] and staged_at[1] == 0 and nbytes >= 1_000_000
+    assert len(copies) == 4 and sum(c[3] for c in copies) == 1_000_000
+    assert all(c[0] == 1 and c[1] % 4096 == 0 and c[2] % 4096 == 0 for c in copies)
+    assert [c[1] - 8192 for c in copies] == [c[2] for c in copies]            # same offset inside the chunk and the slab
+    _s, _n, whole = plan_gather(chunks, rank=0, world=2)
+    assert whole == [(1, 8192, 0, 1_000_000)]

@@ -1186,7 +1186,9 @@ def main() -> None:
                    "on_time_blocks": last.on_time_blocks, "exposed_stall_ms": last.exposed_stall_ms,
                    "delivery": (store.delivery if store is not None and world > 1 else None)}
             if not args.skip_delivery_only:
-                go(1, compute=False, io=False)
+                # two untimed passes: automatic delivery follows wait probes that the host reads a few dozen blocks
+                # after the fact, so the change from a compute-bound to a delivery-bound regime takes a pass to settle
+                go(2, compute=False, io=False)
                 kernel_profile(native)
                 native.lib().sh_stats_reset()
                 ms_d, _ = timed_region(lambda n: go(n, compute=False, io=False), steps, dist_state, None)

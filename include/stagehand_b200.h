@@ -25,7 +25,7 @@
 extern "C" {
 #endif
 
-#define SH_ABI_VERSION 1
+#define SH_ABI_VERSION 2
 
 /* status codes */
 #define SH_OK                 0

@@ -26,6 +26,7 @@ SH_KIND_DEQUANT_I8, SH_KIND_CAST_F32, SH_KIND_COPY, SH_KIND_ZERO = 0, 1, 2, 3
 SH_DT_BF16, SH_DT_F16, SH_DT_F32 = 0, 1, 2
 SH_DESC_PEER_SOURCE = 1
 SH_DESC_ABSOLUTE = 2
+ABI_VERSION = 2                # SH_ABI_VERSION of include/stagehand_b200.h this binding was written against
 SH_NOALLOC_MAX_BYTES = 32 * 1024 * 1024
 MAX_DESCS_PER_LAUNCH = 128     # sq::kMaxDescs
 
@@ -206,8 +207,9 @@ def lib() -> ctypes.CDLL:
         fn = getattr(handle, name)
         fn.argtypes = argtypes
         fn.restype = c_int32
-    if handle.sh_abi_version() != 1:
-        raise TransferError(f"{LIB_PATH.name}: ABI version {handle.sh_abi_version()} != 1")
+    if handle.sh_abi_version() != ABI_VERSION:
+        raise TransferError(f"{LIB_PATH.name}: ABI version {handle.sh_abi_version()} != {ABI_VERSION} "
+                            "(rebuild it: python -m stagehand_b200.build_native)")
     _lib = handle
     return handle
 

@@ -126,8 +126,7 @@ int32_t sh_block_load(uint64_t block, const ShBlockLoad* a) {
     cudaStream_t copy = as_stream(a->copy_stream), copy2 = as_stream(a->copy_stream2), dq = as_stream(a->dequant_stream);
     const void* packed_base = nullptr;
     bool copied = false;
-    cudaEvent_t t0 = nullptr, t1 = nullptr;
-    bool timed = false;
+    CopyTiming timing;
     int64_t copy_bytes = 0;
 
     switch (a->src_kind) {
@@ -136,7 +135,7 @@ int32_t sh_block_load(uint64_t block, const ShBlockLoad* a) {
                 return fail(SH_ERR_INVALID_ARG, "host source: the image and a 256-byte aligned staging slab are required");
             if (a->ev_staging_free != 0)
                 SH_CUDA(cudaStreamWaitEvent(copy, as_event(a->ev_staging_free), 0), "cudaStreamWaitEvent");
-            timed = copy_timing_begin(copy, &t0, &t1);
+            timing.begin(copy);
             copy_bytes = static_cast<int64_t>(b->packed_bytes);
             SH_CUDA(cudaMemcpyAsync(a->staging_dev, a->src, b->packed_bytes, cudaMemcpyHostToDevice, copy), "cudaMemcpyAsync H2D");
             g_ctr.h2d_copies.fetch_add(1, std::memory_order_relaxed);
@@ -160,7 +159,7 @@ int32_t sh_block_load(uint64_t block, const ShBlockLoad* a) {
                 SH_CUDA(cudaStreamWaitEvent(copy, as_event(a->ev_staging_free), 0), "cudaStreamWaitEvent");
                 if (two) SH_CUDA(cudaStreamWaitEvent(copy2, as_event(a->ev_staging_free), 0), "cudaStreamWaitEvent");
             }
-            timed = copy_timing_begin(copy, &t0, &t1);
+            timing.begin(copy);
             uint8_t* staging = static_cast<uint8_t*>(a->staging_dev);
             int64_t bytes = 0;
             for (size_t i = 0; i < b->pieces.size(); ++i) {
@@ -186,7 +185,7 @@ int32_t sh_block_load(uint64_t block, const ShBlockLoad* a) {
     }
 
     if (copied) {
-        if (timed) copy_timing_end(copy, t0, t1, copy_bytes);
+        timing.end(copy_bytes);
         for (uint64_t ev : {a->ev_copied, a->ev_copied2})
             if (ev != 0) SH_CUDA(cudaEventRecord(as_event(ev), copy), "cudaEventRecord");
         if (copy != dq) {

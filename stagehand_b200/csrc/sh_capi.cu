@@ -126,6 +126,12 @@ void copy_timing_end(cudaStream_t stream, cudaEvent_t start, cudaEvent_t stop, i
     g_prof_pending.push_back(ProfRecord{start, stop, 0, bytes, 1});
 }
 
+void copy_timing_abandon(cudaEvent_t start, cudaEvent_t stop) {
+    std::lock_guard<std::mutex> lk(g_prof_mu);
+    g_prof_free.push_back(start);
+    g_prof_free.push_back(stop);
+}
+
 }  // namespace shc
 
 namespace {

@@ -40,6 +40,17 @@ int launch_plans(const sq::BlockPlan* plans, int n_plans, int64_t elements, int6
 // copy_timing_begin returns false (and sets nothing) when profiling is off.
 bool copy_timing_begin(cudaStream_t stream, cudaEvent_t* start_out, cudaEvent_t* stop_out);
 void copy_timing_end(cudaStream_t stream, cudaEvent_t start, cudaEvent_t stop, int64_t bytes);
+void copy_timing_abandon(cudaEvent_t start, cudaEvent_t stop);      // the load failed: the events go back unused
+
+// Brackets the copies of one sh_block_load; whatever path the function leaves by, the events are accounted for.
+struct CopyTiming {
+    cudaStream_t stream = nullptr;
+    cudaEvent_t start = nullptr, stop = nullptr;
+    bool open = false;
+    void begin(cudaStream_t s) { stream = s; open = copy_timing_begin(s, &start, &stop); }
+    void end(int64_t bytes) { if (open) { copy_timing_end(stream, start, stop, bytes); open = false; } }
+    ~CopyTiming() { if (open) copy_timing_abandon(start, stop); }
+};
 
 // Polls an event until done or until the deadline; never blocks without bound.
 int wait_event_bounded(cudaEvent_t ev, int timeout_ms);

@@ -144,6 +144,35 @@ def test_registered_block_reproduces_the_reference_golden_vectors() -> None:
     lib.sh_block_unregister(block)
 
 
+def test_registered_block_with_more_descriptors_than_one_launch_holds() -> None:
+    """300 descriptors = three launch plans kept by one registration; loaded twice into different slabs."""
+    lib = _lib()
+    rng = np.random.default_rng(23)
+    img = HandImage()
+    for i in range(300):
+        rows, cols = 3 + i % 5, 16 * (1 + i % 4)
+        q = rng.integers(-128, 128, size=(rows, cols), dtype=np.int8)
+        img.add_dequant(q, np.exp(rng.standard_normal(rows)).astype(np.float32),
+                        rng.standard_normal(rows).astype(np.float32) if i % 7 == 0 else None, rows, cols, "bf16")
+    host_np = img.host_bytes()
+    out_bytes = align(img.dst_cursor, 256)
+    expect = expand(host_np, img.descs, len(img.descs), out_bytes, DT_CODE["bf16"])
+    block = _register(lib, img, host_np.size, out_bytes)
+    image_dev = torch.from_numpy(host_np).cuda()
+    stream = torch.cuda.current_stream().cuda_stream
+    before = _native.stats()["kernel_launches"]
+    for _ in range(2):
+        out = torch.full((out_bytes,), 0xEE, dtype=torch.uint8, device="cuda")
+        a = ShBlockLoad()
+        a.src, a.out_dev, a.src_kind = image_dev.data_ptr(), out.data_ptr(), _native.SH_SRC_DEVICE
+        a.copy_stream = a.dequant_stream = stream
+        _native.check(lib.sh_block_load(block, ctypes.byref(a)), "sh_block_load")
+        torch.cuda.synchronize()
+        assert np.array_equal(out.cpu().numpy(), expect)
+    assert _native.stats()["kernel_launches"] - before == 6
+    lib.sh_block_unregister(block)
+
+
 def test_registration_and_load_reject_bad_arguments() -> None:
     lib = _lib()
     img = _mixed_image(3)

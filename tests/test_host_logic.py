@@ -26,7 +26,7 @@ def test_library_exports_every_declared_symbol() -> None:
     lib = _native.lib()
     for name in declared:
         assert getattr(lib, name) is not None
-    assert lib.sh_abi_version() == 1
+    assert lib.sh_abi_version() == _native.ABI_VERSION == 2
     assert ctypes.sizeof(_native.ShParamDesc) == 64
 
 

@@ -483,6 +483,13 @@ static inline bool aligned(const void* p, uintptr_t a) { return (reinterpret_cas
 
 static inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
+// [off, off + len) lies inside [0, total): written so that no sum can overflow, whatever the caller passes
+static inline bool in_range(int64_t off, int64_t len, int64_t total) {
+    return off >= 0 && len >= 0 && off <= total && len <= total - off;
+}
+
+constexpr int64_t kMaxCount = int64_t(1) << 40;     // rows x cols, row strides and vector lengths stay below this
+
 static uint32_t gcd_u32(uint32_t a, uint32_t b) {
     while (b != 0) {
         const uint32_t t = a % b;
@@ -563,11 +570,11 @@ int build_plans(const ShParamDesc* descs, int n, const void* packed, size_t pack
         snprintf(err, err_len, __VA_ARGS__);              \
         return SH_ERR_INVALID_ARG;                        \
     } while (0)
-        if (u.dst_off < 0) SQ_FAIL("descriptor %d: negative dst_off", i);
+        if (u.dst_off < 0 || u.dst_off > obytes) SQ_FAIL("descriptor %d: dst_off negative or beyond the output slab", i);
         switch (u.kind) {
             case SH_KIND_DEQUANT_I8: {
                 if (u.rows <= 0 || u.cols <= 0 || u.ld < u.cols) SQ_FAIL("descriptor %d: bad rows/cols/ld", i);
-                if (u.rows > (int64_t(1) << 40) / u.cols) SQ_FAIL("descriptor %d: matrix too large", i);
+                if (u.rows > kMaxCount / u.cols || u.ld > kMaxCount / u.rows) SQ_FAIL("descriptor %d: matrix too large", i);
                 if (absolute) {
                     if (u.src_off <= 0 || u.scale_off <= 0 || u.zp_off == 0)
                         SQ_FAIL("descriptor %d: null absolute source address", i);
@@ -575,11 +582,11 @@ int build_plans(const ShParamDesc* descs, int n, const void* packed, size_t pack
                     D.scale = reinterpret_cast<const float*>(static_cast<uintptr_t>(u.scale_off));
                     D.zp = u.zp_off > 0 ? reinterpret_cast<const float*>(static_cast<uintptr_t>(u.zp_off)) : nullptr;
                 } else {
-                    if (u.src_off < 0 || u.src_off + (u.rows - 1) * u.ld + u.cols > pbytes)
+                    if (!in_range(u.src_off, (u.rows - 1) * u.ld + u.cols, pbytes))
                         SQ_FAIL("descriptor %d: int8 rows outside the packed image", i);
-                    if (u.scale_off < 0 || u.scale_off % 4 != 0 || u.scale_off + u.rows * 4 > pbytes)
+                    if (u.scale_off % 4 != 0 || !in_range(u.scale_off, u.rows * 4, pbytes))
                         SQ_FAIL("descriptor %d: scales outside the packed image or not 4-byte aligned", i);
-                    if (u.zp_off >= 0 && (u.zp_off % 4 != 0 || u.zp_off + u.rows * 4 > pbytes))
+                    if (u.zp_off >= 0 && (u.zp_off % 4 != 0 || !in_range(u.zp_off, u.rows * 4, pbytes)))
                         SQ_FAIL("descriptor %d: zero points outside the packed image or not 4-byte aligned", i);
                     D.src = pbase + u.src_off;
                     D.scale = reinterpret_cast<const float*>(pbase + u.scale_off);
@@ -598,8 +605,8 @@ int build_plans(const ShParamDesc* descs, int n, const void* packed, size_t pack
                     // bulk scale fetch: 16-byte aligned arrays whose 4-row padding stays inside the image
                     const int64_t rows4 = (u.rows + 3) & ~int64_t(3);
                     const bool bulk_ok = !absolute && !(D.flags & SH_DESC_PEER_SOURCE) && aligned(D.scale, 16) &&
-                                         u.scale_off + rows4 * 4 <= pbytes &&
-                                         (D.zp == nullptr || (aligned(D.zp, 16) && u.zp_off + rows4 * 4 <= pbytes));
+                                         in_range(u.scale_off, rows4 * 4, pbytes) &&
+                                         (D.zp == nullptr || (aligned(D.zp, 16) && in_range(u.zp_off, rows4 * 4, pbytes)));
                     if (bulk_ok) D.flags |= kFlagBulkScales;
                     if (osz == 2 && aligned(obase + u.dst_off, 32)) D.flags |= kFlagStore32;
                     if (u.ld == u.cols) D.flags |= kFlagDense;
@@ -616,8 +623,8 @@ int build_plans(const ShParamDesc* descs, int n, const void* packed, size_t pack
                 break;
             }
             case SH_KIND_CAST_F32: {
-                if (u.cols < 0) SQ_FAIL("descriptor %d: negative count", i);
-                if (!absolute && (u.src_off < 0 || u.src_off % 4 != 0 || u.src_off + u.cols * 4 > pbytes))
+                if (u.cols < 0 || u.cols > kMaxCount) SQ_FAIL("descriptor %d: negative or oversized count", i);
+                if (!absolute && (u.src_off % 4 != 0 || !in_range(u.src_off, u.cols * 4, pbytes)))
                     SQ_FAIL("descriptor %d: fp32 source outside the packed image or not 4-byte aligned", i);
                 if (absolute && u.src_off <= 0) SQ_FAIL("descriptor %d: null absolute source address", i);
                 dst_bytes = u.cols * osz;
@@ -632,9 +639,9 @@ int build_plans(const ShParamDesc* descs, int n, const void* packed, size_t pack
             }
             case SH_KIND_COPY:
             case SH_KIND_ZERO: {
-                if (u.cols < 0) SQ_FAIL("descriptor %d: negative byte count", i);
+                if (u.cols < 0 || u.cols > kMaxCount) SQ_FAIL("descriptor %d: negative or oversized byte count", i);
                 const bool zero = u.kind == SH_KIND_ZERO;
-                if (!zero && !absolute && (u.src_off < 0 || u.src_off + u.cols > pbytes))
+                if (!zero && !absolute && !in_range(u.src_off, u.cols, pbytes))
                     SQ_FAIL("descriptor %d: copy source outside the packed image", i);
                 if (!zero && absolute && u.src_off <= 0) SQ_FAIL("descriptor %d: null absolute source address", i);
                 dst_bytes = u.cols;
@@ -652,7 +659,7 @@ int build_plans(const ShParamDesc* descs, int n, const void* packed, size_t pack
         }
         if (u.kind != SH_KIND_COPY && u.kind != SH_KIND_ZERO && !aligned(obase + u.dst_off, osz))
             SQ_FAIL("descriptor %d: destination not aligned to the element size", i);
-        if (u.dst_off + dst_bytes > obytes) SQ_FAIL("descriptor %d: destination outside the output slab", i);
+        if (!in_range(u.dst_off, dst_bytes, obytes)) SQ_FAIL("descriptor %d: destination outside the output slab", i);
         if (tiles + static_cast<uint64_t>(n_tiles) > 0x7FFFFFFFull) SQ_FAIL("descriptor %d: too many tiles", i);
 #undef SQ_FAIL
         D.dst = obase + u.dst_off;

@@ -85,6 +85,10 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--gather-parts", type=int, default=0,
                     help="multi-GPU gather: copies per block at least this many (owners' chunks are cut; 0 = library default)")
     ap.add_argument("--staging-slabs", type=int, default=0, help="INT8 staging slabs in VRAM (0 = prefetch_k + 1)")
+    ap.add_argument("--replicas", action="store_true",
+                    help="multi-GPU control experiment: every rank keeps ALL INT8 images in its own HBM (the 1-GPU value "
+                         "configuration run N times side by side, nothing crosses NVLink): what the forward costs at N busy "
+                         "GPUs before any sharding")
     ap.add_argument("--skip-cfg5", action="store_true", help="multi-GPU: do not append the encoder + DiT pass")
     ap.add_argument("--skip-parity", action="store_true")
     ap.add_argument("--no-wraparound", action="store_true",
@@ -280,6 +284,14 @@ def timed_region(fn, steps: int, dist_state, sampler: ClockSampler | None):
         t = torch.tensor([ms], dtype=torch.float64, device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
+        if sampler:
+            # every rank samples its own GPU; the line carries rank 0's record plus the per-rank medians (the step
+            # time is the maximum over ranks, so the slowest clock counts)
+            mine = [clocks.get("sm_mhz"), ",".join(clocks.get("reasons", []))]
+            gathered = [None] * dist_state["world"]
+            dist.all_gather_object(gathered, mine)
+            clocks["per_rank_sm_mhz"] = [g[0] for g in gathered]
+            clocks["reasons"] = sorted({r for g in gathered for r in g[1].split(",") if r})
     return ms, clocks
 
 
@@ -1152,8 +1164,9 @@ def main() -> None:
             if source == "hbm":
                 from stagehand_b200.sharded import DeviceImageStore
 
-                store = DeviceImageStore(rt, rank=rank, world=world, fused=not args.no_fused,
-                                         layout=args.layout if world > 1 else "owner",
+                shard_world = 1 if args.replicas else world
+                store = DeviceImageStore(rt, rank=0 if args.replicas else rank, world=shard_world, fused=not args.no_fused,
+                                         layout=args.layout if shard_world > 1 else "owner",
                                          peer_ctas_per_sm=args.peer_ctas_per_sm,
                                          gather=args.delivery, peer_deep_loads=args.peer_deep_loads,
                                          gather_parts=args.gather_parts or None)
@@ -1170,7 +1183,7 @@ def main() -> None:
             native.check(native.lib().sh_profile_enable(1))
             kernel_profile(native)
             native.lib().sh_stats_reset()
-            sampler = ClockSampler(local_rank) if rank == 0 else None
+            sampler = ClockSampler(local_rank)
             ms, clocks = timed_region(go, steps, dist_state, sampler)
             prof = kernel_profile(native)
             stats = native.stats()
@@ -1184,7 +1197,7 @@ def main() -> None:
                    "setup_s": setup_phase_s,
                    "gathered_loads": last.gathered_loads, "probed_blocks": last.probed_blocks,
                    "on_time_blocks": last.on_time_blocks, "exposed_stall_ms": last.exposed_stall_ms,
-                   "delivery": (store.delivery if store is not None and world > 1 else None)}
+                   "delivery": (store.delivery if store is not None and world > 1 and not args.replicas else None)}
             if not args.skip_delivery_only:
                 # two untimed passes: automatic delivery follows wait probes that the host reads a few dozen blocks
                 # after the fact, so the change from a compute-bound to a delivery-bound regime takes a pass to settle
@@ -1211,7 +1224,7 @@ def main() -> None:
 
         results["e2e"] = phase("e2e", "host" if world == 1 else "hbm")
         results["value"] = phase("value", "hbm")
-        if world > 1 and not args.skip_cfg5 and args.workload in ("flux", "flux_small"):
+        if world > 1 and not args.skip_cfg5 and not args.replicas and args.workload in ("flux", "flux_small"):
             results["cfg5"] = phase("cfg5", "hbm", workload="flux_mistral" if args.workload == "flux" else "flux_mistral_small",
                                     steps=3, warmup=2)
         setup_s = time.perf_counter() - t_setup
@@ -1236,6 +1249,18 @@ def main() -> None:
         dist.destroy_process_group()
     if failed:
         raise SystemExit("parity check failed: a delivered block differs between ranks or from the oracle (see the line's parity keys)")
+
+
+def clock_normalised(res: dict) -> dict | None:
+    clocks = res.get("clocks") or {}
+    per_rank = [c for c in (clocks.get("per_rank_sm_mhz") or [clocks.get("sm_mhz")]) if c]
+    if not per_rank or not clocks.get("sm_max_mhz"):
+        return None
+    slowest = min(per_rank)
+    ms = res["ms_total"] / res["steps"]
+    return {"sm_mhz_slowest_rank": slowest, "sm_max_mhz": clocks["sm_max_mhz"],
+            "ms_per_step_at_max_clock": ms * slowest / clocks["sm_max_mhz"],
+            "note": "ms_per_step x (median SM clock of the slowest rank under load / maximum SM clock)"}
 
 
 def compose_line(args, world: int, results: dict, peaks: dict, link_peak: float, nvlink_probe: dict | None,
@@ -1314,6 +1339,8 @@ def compose_line(args, world: int, results: dict, peaks: dict, link_peak: float,
                    "l2": "inputs larger than L2 (11.8 GB of INT8 per step); no flush",
                    "value_source": "INT8 images resident in HBM (outside the VRAM budget, which covers the bf16 slabs and the "
                                    "staging ring); the host link is not in this timed region" + ("" if world == 1 else
+                                   f"; CONTROL RUN: {world} replicas side by side, every rank holds all images in its own "
+                                   "HBM and nothing crosses NVLink" if args.replicas else
                                    f"; {args.layout} layout over {world} GPUs, " +
                                    ({"gather": "one copy-engine pull per owner into local staging, then the local block kernel",
                                      "fused": "fused peer-load dequant",
@@ -1329,6 +1356,10 @@ def compose_line(args, world: int, results: dict, peaks: dict, link_peak: float,
                    "weights": ("one int8 tensor set per distinct shape in the slab file, every layer its own scale vector"
                                if not args.unique_weights else "unique per layer")},
         "clocks": v["clocks"],
+        # the forward at N GPUs is bound by the model's own kernels, i.e. by the SM clock each GPU holds under the
+        # board's power cap (which falls as more GPUs of the machine are busy): time x clock separates that from
+        # anything the weight delivery costs
+        "clock_normalised": clock_normalised(v),
         "e2e": {"value": gbs(e, e["ms_total"]), "unit": UNIT, "ms_per_step": e["ms_total"] / K,
                 "h2d_bytes_per_step": e["link_bytes"] + e["input_bytes"], "d2h_bytes_per_step": 4,
                 "peer_bytes_per_step": e["peer_bytes"], "clocks": e["clocks"],

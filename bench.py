@@ -89,6 +89,8 @@ def parse_args() -> argparse.Namespace:
                     help="multi-GPU control experiment: every rank keeps ALL INT8 images in its own HBM (the 1-GPU value "
                          "configuration run N times side by side, nothing crosses NVLink): what the forward costs at N busy "
                          "GPUs before any sharding")
+    ap.add_argument("--skip-control", action="store_true",
+                    help="multi-GPU: do not run the short replicas pass that the sharded forward is compared with")
     ap.add_argument("--skip-cfg5", action="store_true", help="multi-GPU: do not append the encoder + DiT pass")
     ap.add_argument("--skip-parity", action="store_true")
     ap.add_argument("--no-wraparound", action="store_true",
@@ -1155,7 +1157,8 @@ def main() -> None:
         link_peak = probe_host_link()
         nvlink_probe = probe_nvlink(dist_state)
 
-        def phase(name: str, source: str, workload: str | None = None, steps: int = K, warmup: int = W):
+        def phase(name: str, source: str, workload: str | None = None, steps: int = K, warmup: int = W,
+                  replicas: bool = args.replicas, extras: bool = True):
             """One runtime, warm-up, then the timed passes for this weight source ("host" | "hbm")."""
             t_phase = time.perf_counter()
             model, fpk, host_inputs, desc, pattern = build_workload(args, tmp, "cuda", workload)
@@ -1164,8 +1167,8 @@ def main() -> None:
             if source == "hbm":
                 from stagehand_b200.sharded import DeviceImageStore
 
-                shard_world = 1 if args.replicas else world
-                store = DeviceImageStore(rt, rank=0 if args.replicas else rank, world=shard_world, fused=not args.no_fused,
+                shard_world = 1 if replicas else world
+                store = DeviceImageStore(rt, rank=0 if replicas else rank, world=shard_world, fused=not args.no_fused,
                                          layout=args.layout if shard_world > 1 else "owner",
                                          peer_ctas_per_sm=args.peer_ctas_per_sm,
                                          gather=args.delivery, peer_deep_loads=args.peer_deep_loads,
@@ -1197,8 +1200,8 @@ def main() -> None:
                    "setup_s": setup_phase_s,
                    "gathered_loads": last.gathered_loads, "probed_blocks": last.probed_blocks,
                    "on_time_blocks": last.on_time_blocks, "exposed_stall_ms": last.exposed_stall_ms,
-                   "delivery": (store.delivery if store is not None and world > 1 and not args.replicas else None)}
-            if not args.skip_delivery_only:
+                   "delivery": (store.delivery if store is not None and world > 1 and not replicas else None)}
+            if not args.skip_delivery_only and extras:
                 # two untimed passes: automatic delivery follows wait probes that the host reads a few dozen blocks
                 # after the fact, so the change from a compute-bound to a delivery-bound regime takes a pass to settle
                 go(2, compute=False, io=False)
@@ -1209,7 +1212,7 @@ def main() -> None:
                                         "gathered_loads": rt.telemetry.last().gathered_loads,
                                         "loads": rt.telemetry.last().dequant_launches}
             native.check(native.lib().sh_profile_enable(0))
-            if not args.skip_parity:
+            if not args.skip_parity and extras:
                 out["parity"] = parity_check(rt, fpk, dist_state, step[0])
             status = rt._scheduler._streamer.read_status()
             out["kernel_status"] = status
@@ -1224,6 +1227,9 @@ def main() -> None:
 
         results["e2e"] = phase("e2e", "host" if world == 1 else "hbm")
         results["value"] = phase("value", "hbm")
+        if world > 1 and not args.skip_control and not args.replicas:
+            # the same forward with nothing sharded: every rank keeps all images in its own HBM, N replicas side by side
+            results["control"] = phase("control", "hbm", steps=min(K, 10), warmup=min(W, 3), replicas=True, extras=False)
         if world > 1 and not args.skip_cfg5 and not args.replicas and args.workload in ("flux", "flux_small"):
             results["cfg5"] = phase("cfg5", "hbm", workload="flux_mistral" if args.workload == "flux" else "flux_mistral_small",
                                     steps=3, warmup=2)
@@ -1403,6 +1409,16 @@ def compose_line(args, world: int, results: dict, peaks: dict, link_peak: float,
             line["delivery_only"]["host"] = {"value": gbs(e, de["ms_total"]), "ms_per_step": de["ms_total"] / K,
                                              "host_link_gbs": link, "host_link_frac": link / link_peak,
                                              "kernel_hbm": kernel_roof(de["profile"], True)}
+    ctl = results.get("control")
+    if ctl is not None:
+        ctl_ms = ctl["ms_total"] / ctl["steps"]
+        line["replicas_control"] = {
+            "ms_per_step": ctl_ms, "steps": ctl["steps"], "clocks": ctl["clocks"],
+            "sharded_over_control": (v["ms_total"] / K) / ctl_ms,
+            "what": f"the same forward with nothing sharded: each of the {world} ranks keeps all INT8 images in its own HBM "
+                    "(the 1-GPU `value` configuration run side by side, nothing crosses NVLink).  Its distance from a 1-GPU run "
+                    "is what the machine costs with every GPU busy (SM clocks under the power cap); `sharded_over_control` is "
+                    "what sharding the images over the ranks adds on top"}
     c5 = results.get("cfg5")
     if c5 is not None:
         nv5 = nvlink_of(c5)

@@ -84,6 +84,8 @@ def parse_args() -> argparse.Namespace:
                          "while blocks arrive ahead of their use, fused while the compute stream waits for them (auto)")
     ap.add_argument("--gather-parts", type=int, default=0,
                     help="multi-GPU gather: copies per block at least this many (owners' chunks are cut; 0 = library default)")
+    ap.add_argument("--host-copy-streams", type=int, default=2, choices=[1, 2],
+                    help="copy streams host-sourced images alternate between (the library's default is 1)")
     ap.add_argument("--staging-slabs", type=int, default=0, help="INT8 staging slabs in VRAM (0 = prefetch_k + 1)")
     ap.add_argument("--replicas", action="store_true",
                     help="multi-GPU control experiment: every rank keeps ALL INT8 images in its own HBM (the 1-GPU value "
@@ -232,7 +234,8 @@ def make_runtime(args, model, fpk: Path, pattern: str):
         prefetch_window_blocks=args.prefetch_k, eviction_cooldown_steps=0,
         nan_inf_check=False, strict_bf16=False, telemetry_enabled=True, telemetry_interval_steps=0,
         telemetry_file=os.devnull, packed_image_cache_mb=-1, prefetch_wraparound=not args.no_wraparound,
-        dequant_stream_priority=args.dequant_priority, device_staging_slabs=args.staging_slabs)
+        dequant_stream_priority=args.dequant_priority, device_staging_slabs=args.staging_slabs,
+        host_copy_streams=args.host_copy_streams)
     rt = sh.StagehandRuntime(model, cfg, block_pattern=pattern, group="dit", dtype=torch.bfloat16,
                              inference_mode=True)
     converted = rt.convert_registry_to_file_backed(str(fpk))
@@ -925,7 +928,8 @@ def run_module_bf16(args) -> None:
         pinned_pool_mb=2048, pinned_slab_mb=1024, vram_high_watermark_mb=int(budget_mb * 0.8),
         vram_low_watermark_mb=int(budget_mb * 0.6), prefetch_window_blocks=args.prefetch_k, eviction_cooldown_steps=0,
         nan_inf_check=False, strict_bf16=False, telemetry_enabled=True, telemetry_interval_steps=0,
-        telemetry_file=os.devnull, prefetch_wraparound=not args.no_wraparound, pinned_module_mirror=not args.no_mirror)
+        telemetry_file=os.devnull, prefetch_wraparound=not args.no_wraparound, pinned_module_mirror=not args.no_mirror,
+        host_copy_streams=args.host_copy_streams)
     host_inputs = [torch.randn(1, 4096, 3072, generator=g).to(torch.bfloat16).pin_memory(),
                    torch.randn(1, 512, 3072, generator=g).to(torch.bfloat16).pin_memory(),
                    torch.randn(1, 3072, generator=g).to(torch.bfloat16).pin_memory()]
@@ -972,6 +976,7 @@ def run_module_bf16(args) -> None:
                                + (", layer mode (stagehand.layer): every Linear its own unit" if args.layer_mode else ""),
                    "weight_bytes": weight_bytes, "vram_budget_gb": args.vram_budget_gb, "prefetch_k": args.prefetch_k,
                    "pinned_module_mirror": not args.no_mirror, "prefetch_wraparound": not args.no_wraparound,
+                   "host_copy_streams": args.host_copy_streams,
                    "l2": "weights larger than L2; no flush"},
         "clocks": clocks,
         "e2e": {"value": value, "unit": UNIT, "ms_per_step": ms_step,
@@ -1341,7 +1346,8 @@ def compose_line(args, world: int, results: dict, peaks: dict, link_peak: float,
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": v["desc"]["workload"], "arithmetic": "int8 -> fp32 (subtract, multiply) -> bf16, round to nearest even", "vram_budget_gb": args.vram_budget_gb,
                    "prefetch_k": args.prefetch_k,
-                   "prefetch_wraparound": not args.no_wraparound, "int8_elements_per_forward": v["desc"]["int8_elements"],
+                   "prefetch_wraparound": not args.no_wraparound, "host_copy_streams": args.host_copy_streams,
+                   "int8_elements_per_forward": v["desc"]["int8_elements"],
                    "l2": "inputs larger than L2 (11.8 GB of INT8 per step); no flush",
                    "value_source": "INT8 images resident in HBM (outside the VRAM budget, which covers the bf16 slabs and the "
                                    "staging ring); the host link is not in this timed region" + ("" if world == 1 else

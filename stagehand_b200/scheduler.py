@@ -692,7 +692,8 @@ class StagehandScheduler:
         device = torch.device("cuda", torch.cuda.current_device())
         n_staging = self._config.device_staging_slabs or (self._policy.prefetch_window + 1)
         self._streamer = Int8BlockStreamer(device, self._engine.copy_stream, n_staging,
-                                           dequant_priority=self._config.dequant_stream_priority)
+                                           dequant_priority=self._config.dequant_stream_priority,
+                                           host_copy_streams=int(getattr(self._config, "host_copy_streams", 1)))
         pool_kw = dict(on_allocation=getattr(self._budget, "invalidate", None), on_trim=self._view_cache.clear)
         if self._config.device_pool_backend == "vmm":
             from stagehand_b200.device_pool import VmmDeviceSlabPool
@@ -988,8 +989,9 @@ class StagehandScheduler:
         layout = _build_param_layout(module, entry.dtype)
         flat = self._module_mirror(block_id, entry, module, layout)
         res.param_layout = layout
-        out_slab = self._device_pool.acquire(entry.size_bytes, block_id, self._streamer.copy_stream)
-        ticket = self._streamer.submit_plain(block_id, flat.data_ptr(), entry.size_bytes, out_slab)
+        copy_stream = self._streamer.next_host_copy_stream()
+        out_slab = self._device_pool.acquire(entry.size_bytes, block_id, copy_stream)
+        ticket = self._streamer.submit_plain(block_id, flat.data_ptr(), entry.size_bytes, out_slab, copy_stream)
         res.device_slab = out_slab
         res.gpu_tensor = out_slab.tensor[: entry.size_bytes].view(entry.dtype)
         self._pending_handles[block_id] = ticket

@@ -177,7 +177,7 @@ class Int8BlockStreamer:
     """
 
     def __init__(self, device: torch.device, copy_stream: torch.cuda.Stream | None, n_staging: int,
-                 dequant_priority: int = -1) -> None:
+                 dequant_priority: int = -1, host_copy_streams: int = 1) -> None:
         self.device = device
         lib = _native.lib()
         _native.check(lib.sh_init(device.index if device.index is not None else torch.cuda.current_device()), "sh_init")
@@ -192,6 +192,9 @@ class Int8BlockStreamer:
         self._dyn_resident: dict[str, _DynResident] = {}
         self._args = _native.ShBlockLoad()
         self._status_bits = 0
+        # host-sourced images may alternate between two copy streams, so that one copy's tail overlaps the next one's start
+        self._host_copy_streams = max(1, min(2, int(host_copy_streams)))
+        self._host_loads = 0
 
     # ── staging ──────────────────────────────────────────────────────
 
@@ -257,11 +260,11 @@ class Int8BlockStreamer:
 
     def _load(self, reg: _Registered, what: str, *, src: int, kind: int, staging: int, out_slab: DeviceSlab,
               staging_free: int = 0, src_ready: int = 0, copied: int = 0, copied2: int = 0, ready: int = 0,
-              ready2: int = 0, ready3: int = 0, two_copy_streams: bool = False) -> None:
+              ready2: int = 0, ready3: int = 0, two_copy_streams: bool = False, copy_stream=None) -> None:
         a = self._args
         a.src, a.staging_dev, a.out_dev = src or None, staging or None, out_slab.tensor.data_ptr()
         a.status_dev = self.status.data_ptr()
-        a.copy_stream = stream_handle(self.copy_stream)
+        a.copy_stream = stream_handle(copy_stream if copy_stream is not None else self.copy_stream)
         a.copy_stream2 = stream_handle(self.copy_stream2) if two_copy_streams and self.copy_stream2 is not None else 0
         a.dequant_stream = stream_handle(self.dequant_stream)
         a.ev_staging_free, a.ev_src_ready = staging_free, src_ready
@@ -289,21 +292,37 @@ class Int8BlockStreamer:
                              image.total_bytes, image.out_bytes, image.out_dtype_code, keepalive=image)
         if host.last_copy is None:
             host.last_copy = Event(False)           # the image's own, for good (see _take_staging)
+        copy_stream = self.next_host_copy_stream()
         self._load(reg, f"sh_block_load({image.block_id})", src=host.buffer.data_ptr(), kind=_native.SH_SRC_HOST,
                    staging=staging.tensor.data_ptr(), out_slab=out_slab, staging_free=staging_free,
                    copied=copied.handle, copied2=host.last_copy.handle, ready=ready.handle,
-                   ready2=staging.last_use.handle)
+                   ready2=staging.last_use.handle, copy_stream=copy_stream)
         return StreamTicket(image.block_id, ready, copied, link_bytes=image.total_bytes, launches=reg.launches)
 
-    def submit_plain(self, block_id: str, host_ptr: int, nbytes: int, out_slab: DeviceSlab) -> StreamTicket:
-        """A block already in the runtime dtype in page-locked memory: one DMA straight into its slab, no kernel."""
+    def next_host_copy_stream(self) -> torch.cuda.Stream:
+        """The copy stream the next host-sourced image goes on (they alternate when two are configured)."""
+        if self._host_copy_streams < 2:
+            return self.copy_stream
+        self._host_loads += 1
+        if self._host_loads & 1:
+            if self.copy_stream2 is None:
+                self.copy_stream2 = torch.cuda.Stream(device=self.device, priority=-1)
+            return self.copy_stream2
+        return self.copy_stream
+
+    def submit_plain(self, block_id: str, host_ptr: int, nbytes: int, out_slab: DeviceSlab,
+                     copy_stream: torch.cuda.Stream | None = None) -> StreamTicket:
+        """A block already in the runtime dtype in page-locked memory: one DMA straight into its slab, no kernel.
+
+        *copy_stream* is the stream the slab was acquired for (default: the first copy stream)."""
+        stream = copy_stream if copy_stream is not None else self.copy_stream
         if out_slab.last_use is not None:
-            out_slab.last_use.block_stream(self.copy_stream)       # previous readers of the slab are done
+            out_slab.last_use.block_stream(stream)                 # previous readers of the slab are done
             release_event(out_slab.last_use)
             out_slab.last_use = None
         _native.check(self._lib.sh_copy_h2d_async(out_slab.tensor.data_ptr(), host_ptr, nbytes,
-                                                  stream_handle(self.copy_stream)), f"sh_copy_h2d_async({block_id})")
-        ready = acquire_event().record(self.copy_stream)
+                                                  stream_handle(stream)), f"sh_copy_h2d_async({block_id})")
+        ready = acquire_event().record(stream)
         return StreamTicket(block_id, ready, None, link_bytes=nbytes, launches=0)
 
     def submit_from_device(self, image: PackedBlockImage, source: DeviceSource, fused: bool,

@@ -357,6 +357,42 @@ def _module_backed(tmp_path: Path, mirror: bool, **cfg_kw):
     return model, rt
 
 
+def test_two_host_copy_streams_deliver_the_same_bytes(tmp_path: Path) -> None:
+    """``host_copy_streams=2``: consecutive images travel on alternating copy streams; every block image is still the
+    reference's, pass after pass under a budget that evicts every block, and so is a module-backed block's."""
+    model, rt, x = _build("cfg1", tmp_path, host_copy_streams=2, vram_high_watermark_mb=2, vram_low_watermark_mb=1,
+                          eviction_cooldown_steps=0)
+    want = [str(d) for d in G["cfg1__block_sha256"]]
+    seen: dict[int, str] = {}
+    for i, block in enumerate(model.blocks):
+        block.register_forward_hook(lambda mod, _a, _o, i=i: seen.__setitem__(
+            i, hashlib.sha256(rt._residency.get_entry(f"blocks.{i}").gpu_tensor.view(torch.uint8).cpu().numpy().tobytes()).hexdigest()))
+    for step in range(3):
+        seen.clear()
+        rt.begin_step(step)
+        with torch.inference_mode(), rt.managed_forward():
+            y = model(x)
+        rt.end_step()
+        assert [seen[i] for i in range(4)] == want, step
+    assert _rel_l2(y, "cfg1") <= 1e-2
+    streamer = rt._scheduler._streamer
+    assert streamer.copy_stream2 is not None and streamer.read_status() == 0
+    rt.shutdown()
+    # module-backed blocks (one plain DMA per load) alternate too: same outputs as with one stream
+    xm = torch.randn(1, 32, 256, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16)
+    outs = []
+    for streams in (1, 2):
+        m2, rt2 = _module_backed(tmp_path, True, vram_high_watermark_mb=2, vram_low_watermark_mb=1, host_copy_streams=streams)
+        for step in range(2):
+            rt2.begin_step(step)
+            with torch.inference_mode(), rt2.managed_forward():
+                out = m2(xm.cuda()).float().cpu()
+            rt2.end_step()
+        outs.append(out)
+        rt2.shutdown()
+    assert torch.equal(outs[0], outs[1])
+
+
 def test_module_backed_blocks_stream_from_a_pinned_mirror(tmp_path: Path) -> None:
     """Module-backed inference with ``pinned_module_mirror``: same outputs as the reference's copy path, one DMA per
     load, nothing copied back at eviction, and the module is a working CPU model again after shutdown."""

@@ -1434,6 +1434,9 @@ def compose_line(args, world: int, results: dict, peaks: dict, link_peak: float,
                         "delivery_only_ms_per_step": (c5["delivery_only"]["ms_total"] / c5["steps"]) if "delivery_only" in c5 else None,
                         "nvlink_gbs_per_gpu": nv5.get("delivery_only_gbs_per_gpu") if nv5 else None,
                         "nvlink_frac": nv5.get("delivery_only_frac_of_probed") if nv5 else None,
+                        "gathered_loads_of_loads": [c5["gathered_loads"], c5["stats"]["kernel_launches"] // max(c5["steps"], 1)],
+                        "on_time_of_probed_blocks": [c5["on_time_blocks"], c5["probed_blocks"]],
+                        "exposed_stall_ms": c5["exposed_stall_ms"],
                         "kernel_hbm": kernel_roof(c5["profile"], False), "kernel_status": c5["kernel_status"],
                         "parity": c5.get("parity"), "setup_s": c5["setup_s"]}
     return line

@@ -1251,7 +1251,7 @@ def main() -> None:
         print(json.dumps(line), flush=True)
         failed = any(p is not None and not (p["ranks_equal"] and p["oracle_equal"])
                      for p in (res.get("parity") for res in results.values()))
-        if any(res.get("kernel_status") for res in results.values()):
+        if any(int(res.get("kernel_status") or 0) & 2 for res in results.values()):     # a descriptor was skipped on the device
             failed = True
     if world > 1:
         import torch.distributed as dist
@@ -1259,7 +1259,8 @@ def main() -> None:
         dist.barrier()
         dist.destroy_process_group()
     if failed:
-        raise SystemExit("parity check failed: a delivered block differs between ranks or from the oracle (see the line's parity keys)")
+        raise SystemExit("parity check failed: a delivered block differs between ranks or from the oracle, or the block "
+                         "kernel skipped a descriptor (see the line's parity and telemetry keys)")
 
 
 def clock_normalised(res: dict) -> dict | None:

@@ -312,7 +312,10 @@ typedef struct ShBlockLoad {
  *   dequant stream:  wait for the copies, ev_out_free and ev_src_ready; block kernel; record ev_ready
  * Descriptors flagged SH_DESC_ABSOLUTE keep their addresses; the others are offsets into whatever image the
  * load names (staging_dev, or src for SH_SRC_DEVICE).  A failed call may have queued its copies already; it
- * never launches a kernel on bad arguments.
+ * never launches a kernel on bad arguments.  Handles are independent of one another and of the calling thread,
+ * but one handle is not synchronised internally: do not call sh_block_set_gather or sh_block_unregister on it
+ * while another thread is inside sh_block_load for the same handle.  Unregistering a block whose loads are
+ * still running on the GPU is fine (everything a launch needs was handed over when it was queued).
  *
  * Replaces, per block load, _stage_block_to_host + submit_h2d (src/stagehand/scheduler.py:953-987,
  * src/stagehand/transfer.py:108-143); registration replaces TransferEngine::register_block

@@ -111,6 +111,8 @@ def parse_args() -> argparse.Namespace:
                     help="multi-GPU: CTAs per SM a block-kernel launch that reads peer memory may occupy (0 = no cap)")
     ap.add_argument("--peer-deep-loads", action="store_true",
                     help="multi-GPU, fused delivery: the block-kernel variant with 8 loads in flight per thread, 4 CTAs per SM")
+    ap.add_argument("--peer-bulk-loads", action="store_true",
+                    help="multi-GPU, fused delivery: tiles in a peer's arena arrive by one bulk asynchronous copy each")
     ap.add_argument("--dequant-priority", type=int, default=-1, help="CUDA priority of the block kernel's stream")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--skip-delivery-only", action="store_true")
@@ -1177,6 +1179,7 @@ def main() -> None:
                                          layout=args.layout if shard_world > 1 else "owner",
                                          peer_ctas_per_sm=args.peer_ctas_per_sm,
                                          gather=args.delivery, peer_deep_loads=args.peer_deep_loads,
+                                         peer_bulk_loads=args.peer_bulk_loads,
                                          gather_parts=args.gather_parts or None)
             device_inputs = [t.cuda() for t in host_inputs]
             host_io = name == "e2e"

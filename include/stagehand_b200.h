@@ -384,6 +384,15 @@ int32_t sh_set_peer_ctas_per_sm(int32_t ctas_per_sm);
 int32_t sh_set_peer_deep_loads(int32_t on);
 
 /*
+ * Another variant for blocks that read another GPU's memory: every 8 KiB tile that lies in a peer's arena is
+ * fetched with ONE bulk asynchronous copy (cp.async.bulk, the SM's TMA engine; never multicast) into shared
+ * memory, completion counted on an mbarrier and waited for with a bound -- on a time-out the tile is read with
+ * plain loads instead and a status bit is set.  Applies to plans built (or blocks registered) after the call;
+ * off by default; results are identical either way.  No counterpart in the reference.
+ */
+int32_t sh_set_peer_bulk_loads(int32_t on);
+
+/*
  * Per-launch device timing of the block kernel (CUDA events on the launching
  * stream).  While enabled every launch is bracketed by a pair of timing events;
  * sh_profile_collect waits for them (bounded) and returns the sums since the

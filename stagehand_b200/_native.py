@@ -177,6 +177,7 @@ _SIGNATURES: dict[str, list] = {
     "sh_vram_pool_destroy": [c_uint64],
     "sh_set_peer_ctas_per_sm": [c_int32],
     "sh_set_peer_deep_loads": [c_int32],
+    "sh_set_peer_bulk_loads": [c_int32],
     "sh_profile_enable": [c_int32],
     "sh_profile_collect": [POINTER(c_double), POINTER(c_int64), POINTER(c_int64), POINTER(c_int64), c_int32],
     "sh_profile_poll": [POINTER(ShProfileSums)],

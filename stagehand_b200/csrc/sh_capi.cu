@@ -554,6 +554,11 @@ int32_t sh_set_peer_deep_loads(int32_t on) {
     return SH_OK;
 }
 
+int32_t sh_set_peer_bulk_loads(int32_t on) {
+    sq::set_peer_bulk_loads(on != 0);
+    return SH_OK;
+}
+
 int32_t sh_profile_enable(int32_t on) {
     g_prof_on.store(on ? 1 : 0);
     return SH_OK;

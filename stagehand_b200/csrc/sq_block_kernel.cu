@@ -201,9 +201,9 @@ __device__ __forceinline__ uint32_t tile_row_of(uint32_t t, uint32_t spr, uint64
     return t >= spr ? 1u : 0u;
 }
 
-template <typename OutT, bool HasZp, bool Dense, int kSegsPerThread>
+template <typename OutT, bool HasZp, bool Dense, int kSegsPerThread, bool Bulk = false>
 __device__ __forceinline__ void dequant_vec_tile(const DescDev& D, int64_t local_tile, float* s_scale, float* s_zp,
-                                                 uint64_t* s_bar, int32_t* status, bool may_stage) {
+                                                 uint64_t* s_bar, int32_t* status, bool may_stage, int4* s_tile = nullptr) {
     constexpr int kTileSegs = kThreads * kSegsPerThread;       // shadows the namespace constants: this variant's tile
     const uint32_t spr = static_cast<uint32_t>(D.segs_per_row);
     const uint64_t magic = D.row_magic;
@@ -220,16 +220,35 @@ __device__ __forceinline__ void dequant_vec_tile(const DescDev& D, int64_t local
     int64_t row_first;
     uint32_t cseg_first;
 
+    bool bulk_timed_out = false;
     if (Dense) {
         // Contiguous rows: the address of a vector does not depend on its row, so every load is
         // issued before any index arithmetic; rows are only needed to pick the scale.
         const uint8_t* base = D.src + seg0 * kSegBytes;
+        bool from_smem = false;
+        if (Bulk && peer) {
+            // The whole tile (contiguous in the peer's memory) in one bulk asynchronous copy into shared memory:
+            // the copy engine of the SM issues the NVLink reads instead of 128 threads' worth of 16-byte loads.
+            // No multicast; completion is counted on the CTA's mbarrier and waited for with a bound.
+            if (threadIdx.x == 0) {
+                mbar_init(s_bar, 1);
+                mbar_init_fence();
+                mbar_arrive_expect_tx(s_bar, n_segs * kSegBytes);
+                bulk_copy_g2s(s_tile, base, n_segs * kSegBytes, s_bar);
+            }
+            __syncthreads();   // barrier initialised before anyone polls it
+            from_smem = mbar_wait_bounded(s_bar, 0);
+            if (!from_smem) {
+                bulk_timed_out = true;      // fall back to plain loads below; the result stays correct
+                if (status != nullptr) atomicOr(status, kStatusBulkTimeout);
+            }
+        }
 #pragma unroll
         for (int i = 0; i < kSegsPerThread; ++i) {
             const uint32_t o = threadIdx.x + i * kThreads;
             if (o < n_segs) {
                 const uint8_t* p = base + static_cast<uint32_t>(o * kSegBytes);
-                q[i] = peer ? load_plain16(p) : load_stream16(p);
+                q[i] = from_smem ? s_tile[o] : (peer ? load_plain16(p) : load_stream16(p));
             } else {
                 q[i] = make_int4(0, 0, 0, 0);
             }
@@ -303,7 +322,7 @@ __device__ __forceinline__ void dequant_vec_tile(const DescDev& D, int64_t local
     }
     // A copy that was still in flight when the wait gave up targets this CTA's shared
     // memory: give it one more bounded chance to land before the CTA retires.
-    if (timed_out) (void)mbar_wait_bounded(s_bar, 0);
+    if (timed_out || bulk_timed_out) (void)mbar_wait_bounded(s_bar, 0);
 }
 
 template <typename OutT>
@@ -376,12 +395,14 @@ __device__ __forceinline__ void copy_zero_tile(const DescDev& D, int64_t local_t
 
 // ── the kernel ───────────────────────────────────────────────────────────
 
-template <typename OutT, bool GridStride, int Segs>
+template <typename OutT, bool GridStride, int Segs, bool Bulk = false>
 __global__ void __launch_bounds__(kThreads, (GridStride || Segs != kSegsPerThread) ? kDeepMinCtasPerSm : SQ_MIN_CTAS_PER_SM)
 sq_block_kernel(const __grid_constant__ BlockPlan plan, int32_t* status) {
     __shared__ alignas(16) float s_scale[kSmemRows];
     __shared__ alignas(16) float s_zp[kSmemRows];
     __shared__ alignas(8) uint64_t s_bar;
+    // landing area of a tile fetched from a peer GPU with one bulk copy (the Bulk instantiation only)
+    __shared__ alignas(128) int4 s_tile[Bulk ? kThreads * Segs : 1];
 
     // One tile per CTA when the grid covers the launch; a capped grid (launches that read a peer GPU's
     // memory, see launch_plan) walks the tiles grid-stride.  Only a CTA with a single tile stages scales
@@ -404,8 +425,8 @@ sq_block_kernel(const __grid_constant__ BlockPlan plan, int32_t* status) {
     switch (D.path) {
         case kPathDequantVec:
             if (D.flags & kFlagDense) {
-                if (D.zp != nullptr) dequant_vec_tile<OutT, true, true, Segs>(D, local_tile, s_scale, s_zp, &s_bar, status, single);
-                else                 dequant_vec_tile<OutT, false, true, Segs>(D, local_tile, s_scale, s_zp, &s_bar, status, single);
+                if (D.zp != nullptr) dequant_vec_tile<OutT, true, true, Segs, Bulk>(D, local_tile, s_scale, s_zp, &s_bar, status, single, s_tile);
+                else                 dequant_vec_tile<OutT, false, true, Segs, Bulk>(D, local_tile, s_scale, s_zp, &s_bar, status, single, s_tile);
             } else {
                 if (D.zp != nullptr) dequant_vec_tile<OutT, true, false, Segs>(D, local_tile, s_scale, s_zp, &s_bar, status, single);
                 else                 dequant_vec_tile<OutT, false, false, Segs>(D, local_tile, s_scale, s_zp, &s_bar, status, single);
@@ -431,6 +452,10 @@ sq_block_kernel(const __grid_constant__ BlockPlan plan, int32_t* status) {
 static std::atomic<int> g_peer_ctas_per_sm{0};
 static std::atomic<int> g_sm_count{0};
 static std::atomic<bool> g_peer_deep{false};
+static std::atomic<bool> g_peer_bulk{false};
+
+void set_peer_bulk_loads(bool on) { g_peer_bulk.store(on); }
+bool peer_bulk_loads() { return g_peer_bulk.load(); }
 
 void set_peer_deep_loads(bool on) { g_peer_deep.store(on); }
 bool peer_deep_loads() { return g_peer_deep.load(); }
@@ -460,9 +485,11 @@ cudaError_t launch_plan(const BlockPlan& plan, int out_dtype, cudaStream_t strea
     const dim3 grid(ctas), block(kThreads);
     const bool stride = ctas < static_cast<unsigned>(plan.total_tiles);
     const bool deep = plan.segs_per_thread == static_cast<uint32_t>(kDeepSegsPerThread);
+    const bool bulk = plan.bulk_peer != 0 && !deep && !stride;
 #define SQ_LAUNCH(T)                                                                                              \
     do {                                                                                                          \
-        if (deep && stride)  sq_block_kernel<T, true, kDeepSegsPerThread><<<grid, block, 0, stream>>>(plan, status_dev);   \
+        if (bulk)            sq_block_kernel<T, false, kSegsPerThread, true><<<grid, block, 0, stream>>>(plan, status_dev); \
+        else if (deep && stride)  sq_block_kernel<T, true, kDeepSegsPerThread><<<grid, block, 0, stream>>>(plan, status_dev);   \
         else if (deep)       sq_block_kernel<T, false, kDeepSegsPerThread><<<grid, block, 0, stream>>>(plan, status_dev);  \
         else if (stride)     sq_block_kernel<T, true, kSegsPerThread><<<grid, block, 0, stream>>>(plan, status_dev);       \
         else                 sq_block_kernel<T, false, kSegsPerThread><<<grid, block, 0, stream>>>(plan, status_dev);      \
@@ -557,6 +584,7 @@ int build_plans(const ShParamDesc* descs, int n, const void* packed, size_t pack
             plan = &plans_out[n_plans++];
             memset(plan, 0, sizeof(BlockPlan));
             plan->segs_per_thread = static_cast<uint32_t>(segs);
+            plan->bulk_peer = (reads_peer && peer_bulk_loads() && segs == kSegsPerThread) ? 1u : 0u;
             tiles = 0;
         }
         DescDev D;

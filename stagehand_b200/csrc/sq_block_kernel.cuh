@@ -78,6 +78,8 @@ struct BlockPlan {
     int32_t  total_tiles;
     uint32_t tile_stride;                 // CTA b works on tile (b * tile_stride) mod total_tiles; 1 = in order.
     uint32_t segs_per_thread;             // vector loads per thread of the dequant tiles (kSegsPerThread or kDeepSegsPerThread)
+    uint32_t bulk_peer;                   // 1: tiles read from a peer GPU arrive by one bulk asynchronous copy each
+    uint32_t pad2_;
                                           // A stride coprime with total_tiles scatters neighbouring CTAs over the
                                           // whole launch, so a launch that reads from several GPUs pulls from all
                                           // of them at once instead of one stripe (one peer) at a time.
@@ -111,5 +113,10 @@ int peer_ctas_per_sm();
 // Whether plans that read another GPU's memory are built for the deep variant (off by default).
 void set_peer_deep_loads(bool on);
 bool peer_deep_loads();
+
+// Whether tiles read from another GPU's memory are fetched with one bulk asynchronous copy (TMA engine, no
+// multicast, bounded wait) into shared memory instead of per-thread 16-byte loads (off by default).
+void set_peer_bulk_loads(bool on);
+bool peer_bulk_loads();
 
 }  // namespace sq

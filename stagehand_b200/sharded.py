@@ -222,7 +222,8 @@ class DeviceImageStore:
 
     def __init__(self, runtime: Any, rank: int = 0, world: int = 1, layout: str = "owner", fused: bool = True,
                  group: Any = None, emulate_world: int = 0, peer_ctas_per_sm: int | None = None,
-                 gather: bool | str = False, peer_deep_loads: bool | None = None, gather_parts: int | None = None) -> None:
+                 gather: bool | str = False, peer_deep_loads: bool | None = None, gather_parts: int | None = None,
+                 peer_bulk_loads: bool | None = None) -> None:
         if not torch.cuda.is_available():
             raise TransferError("device-resident images need a CUDA device")
         if peer_deep_loads is not None:
@@ -231,6 +232,9 @@ class DeviceImageStore:
         if peer_ctas_per_sm is not None:
             # process-wide: how much of each SM a kernel that reads peer memory may occupy (0 = no cap)
             _native.check(_native.lib().sh_set_peer_ctas_per_sm(int(peer_ctas_per_sm)), "sh_set_peer_ctas_per_sm")
+        if peer_bulk_loads is not None:
+            # process-wide: tiles that lie in a peer's arena arrive by one bulk asynchronous copy each
+            _native.check(_native.lib().sh_set_peer_bulk_loads(1 if peer_bulk_loads else 0), "sh_set_peer_bulk_loads")
         if layout not in ("owner", "striped"):
             raise ValueError(f"unknown shard layout {layout!r}")
         self._lib = _native.lib()

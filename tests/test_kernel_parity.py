@@ -219,6 +219,33 @@ def test_deep_load_variant_for_peer_sources_matches(cap: int) -> None:
         _assert_same(out[off : off + ref.size], ref, "bf16")
 
 
+@pytest.mark.parametrize("rt", ["bf16", "f32"])
+def test_bulk_copy_variant_for_peer_sources_matches(rt: str) -> None:
+    """Tiles of a peer-sourced matrix fetched with one bulk asynchronous copy each into shared memory: same bytes;
+    full and ragged last tiles, zero points, a matrix with padded rows (which takes the per-thread path), and local
+    descriptors in the same launch."""
+    rng = np.random.default_rng(31)
+    lib = _native.lib()
+    img = HandImage()
+    cases = []
+    for rows, cols, with_zp, pad, peer in ((3000, 4096, False, 0, True), (1537, 2048, True, 0, True), (40000, 64, False, 0, True),
+                                           (9, 1008, True, 0, True), (2049, 1024, False, 64, True), (1, 16, False, 0, True),
+                                           (777, 512, True, 0, False)):
+        q = rng.integers(-128, 128, size=(rows, cols + pad), dtype=np.int8)
+        scale = np.exp(rng.standard_normal(rows)).astype(np.float32)
+        zp = rng.standard_normal(rows).astype(np.float32) if with_zp else None
+        cases.append((img.add_dequant(q, scale, zp, rows, cols, rt, peer=peer), q, scale, zp, rows, cols))
+    try:
+        _native.check(lib.sh_set_peer_bulk_loads(1))
+        out, status = run_block(img, rt)
+    finally:
+        _native.check(lib.sh_set_peer_bulk_loads(0))
+    assert status == 0
+    for off, q, scale, zp, rows, cols in cases:
+        ref = oracle.dequant_rows(q, scale, zp, rows, cols, rt)
+        _assert_same(out[off : off + ref.size], ref, rt)
+
+
 def test_bad_descriptors_are_rejected_before_launch() -> None:
     lib = _native.lib()
     _native.check(lib.sh_init(torch.cuda.current_device()))

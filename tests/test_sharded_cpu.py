@@ -209,3 +209,88 @@ def test_close_waits_for_every_rank_before_unmapping_or_freeing(tmp_path) -> Non
     world = 2
     mp.spawn(_close_rank_main, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     assert (tmp_path / "ordered").exists()
+
+
+def test_random_blocks_stripe_and_gather_back_to_the_same_bytes() -> None:
+    """Property test (hypothesis): for any mix of weight shapes and any world size, the stripes of a block cover
+    every output byte exactly once, stay inside their chunks, keep 16-byte alignment, and a consumer that gathers the
+    remote chunks (whole or cut into parts) expands the same bytes as the unsharded image."""
+    from hypothesis import given, settings
+    from hypothesis import strategies as st
+
+    from desc_interp import expand
+    from stagehand_b200 import _native
+    from stagehand_b200._native import ShParamDesc
+    from stagehand_b200.sharded import plan_block_stripes, plan_gather
+
+    shapes = st.lists(st.tuples(st.integers(1, 70), st.sampled_from([16, 32, 48, 64, 160]), st.booleans()),
+                      min_size=1, max_size=4)
+
+    @settings(max_examples=40, deadline=None)
+    @given(shapes=shapes, world=st.integers(1, 8), min_copies=st.integers(1, 5), seed=st.integers(0, 2**16),
+           with_bias=st.booleans())
+    def check(shapes, world, min_copies, seed, with_bias) -> None:
+        rng = np.random.default_rng(seed)
+        image = np.zeros(1 << 17, dtype=np.uint8)
+        descs, cursor, dst = [], 0, 0
+
+        def put(data: np.ndarray, align: int) -> int:
+            nonlocal cursor
+            cursor = -(-cursor // align) * align
+            raw = np.ascontiguousarray(data).view(np.uint8).reshape(-1)
+            image[cursor : cursor + raw.size] = raw
+            at = cursor
+            cursor += -(-raw.size // 16) * 16 + 16
+            return at
+
+        for rows, cols, with_zp in shapes:
+            q = put(rng.integers(-128, 128, size=(rows, cols), dtype=np.int8), 256)
+            s = put(np.exp(rng.standard_normal(rows)).astype(np.float32), 16)
+            z = put(rng.standard_normal(rows).astype(np.float32), 16) if with_zp else -1
+            descs.append(ShParamDesc(kind=_native.SH_KIND_DEQUANT_I8, flags=0, src_off=q, scale_off=s, zp_off=z, dst_off=dst,
+                                     rows=rows, cols=cols, ld=cols))
+            dst += rows * cols * 2
+        if with_bias:
+            b = put(rng.standard_normal(24).astype(np.float32), 16)
+            descs.append(ShParamDesc(kind=_native.SH_KIND_CAST_F32, flags=0, src_off=b, scale_off=0, zp_off=-1, dst_off=dst,
+                                     rows=1, cols=24, ld=0))
+            dst += 48
+        expected = expand(image, descs, len(descs), dst, _native.SH_DT_BF16)
+
+        arena_cursor = [int(v) for v in rng.integers(0, 9000, size=world)]       # earlier blocks left the cursors anywhere
+        stripes = plan_block_stripes(descs, 2, world, home_rank=int(rng.integers(0, world)), arena_cursor=arena_cursor)
+        arenas = [np.zeros(arena_cursor[r] + 64, dtype=np.uint8) for r in range(world)]
+        for p in stripes.pieces:
+            start, end = stripes.chunks[p.rank]
+            assert start <= p.arena_off and p.arena_off + p.nbytes <= end and start % 4096 == 0
+            arenas[p.rank][p.arena_off : p.arena_off + p.nbytes] = image[p.full_off : p.full_off + p.nbytes]
+        covered = np.zeros(dst, dtype=np.int32)
+        for d in stripes.descs:
+            nbytes = d.rows * d.cols * 2 if d.kind in (_native.SH_KIND_DEQUANT_I8, _native.SH_KIND_CAST_F32) else d.cols
+            covered[d.dst_off : d.dst_off + nbytes] += 1
+            assert d.src_off % 16 == 0 and d.scale_off % 16 == 0
+        assert np.all(covered == 1)
+
+        consumer = int(rng.integers(0, world))
+        staged_at, staging_bytes, copies = plan_gather(stripes.chunks, consumer, world, min_copies)
+        staging = np.full(staging_bytes + 64, 0xAB, dtype=np.uint8)
+        for owner, at, staged, nbytes in copies:
+            assert owner != consumer and at % 4096 == 0 and staged % 4096 == 0 and nbytes > 0
+            staging[staged : staged + nbytes] = arenas[owner][at : at + nbytes]
+        moved = {}
+        for owner, _at, _staged, nbytes in copies:
+            moved[owner] = moved.get(owner, 0) + nbytes
+        assert moved == {r: e - s for r, (s, e) in stripes.chunks.items() if r != consumer}   # whole chunks, once
+        out = np.full(dst, 0xEE, dtype=np.uint8)
+        for d in stripes.descs:
+            local = d.rank == consumer
+            shift = 0 if local else staged_at[d.rank] - stripes.chunks[d.rank][0]
+            one = ShParamDesc(kind=d.kind, flags=0, src_off=d.src_off + shift, scale_off=d.scale_off + shift,
+                              zp_off=d.zp_off + shift if d.zp_off >= 0 else -1, dst_off=d.dst_off, rows=d.rows, cols=d.cols,
+                              ld=d.ld)
+            part = expand(arenas[d.rank] if local else staging, [one], 1, dst, _native.SH_DT_BF16)
+            nbytes = d.rows * d.cols * 2 if d.kind in (_native.SH_KIND_DEQUANT_I8, _native.SH_KIND_CAST_F32) else d.cols
+            out[d.dst_off : d.dst_off + nbytes] = part[d.dst_off : d.dst_off + nbytes]
+        assert np.array_equal(out, expected)
+
+    check()
